@@ -96,6 +96,11 @@ typedef struct nb_attn_bwd_args {
   void* workspace;
   size_t workspace_bytes;
   int32_t* status;
+  /* Optional profiling hooks: cudaEvent_t handles (or NULL) recorded on `stream` immediately
+   * before and after the main backward kernel, i.e. between the row-dot prologue and the dQ
+   * conversion epilogue, so a caller can time the dominant kernel alone. */
+  void* event_main_begin;
+  void* event_main_end;
 } nb_attn_bwd_args;
 
 int nb_attn_bwd(const nb_attn_bwd_args* args, void* stream);

@@ -74,6 +74,8 @@ class BwdArgs(C.Structure):
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p),
+        ("event_main_begin", C.c_void_p),
+        ("event_main_end", C.c_void_p),
     ]
 
 

@@ -174,7 +174,7 @@ int nb_attn_fwd(const nb_attn_fwd_args* a, void* stream) {
   p.scale_log2 = s.scale * kLog2e;
   p.status = a->status;
 
-  const dim3 grid(ceil_div(s.max_seqlen_q, nb::kTile), s.heads, s.batch);
+  const dim3 grid(ceil_div(s.max_seqlen_q, nb::kFwdQRows), s.heads, s.batch);
   nb::attn_fwd_kernel<<<grid, nb::kFwdThreads, nb::kFwdSmemBytes, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? NB_ATTN_OK : NB_ATTN_ERR_LAUNCH;
 }
@@ -239,8 +239,10 @@ int nb_attn_bwd(const nb_attn_bwd_args* a, void* stream) {
   const int64_t want_blocks = (rows * 8 + 255) / 256;
   const int aux_blocks = int(want_blocks < 148 * 16 ? want_blocks : 148 * 16);
   nb::attn_bwd_prologue_kernel<<<aux_blocks, 256, 0, st>>>(p);
+  if (a->event_main_begin) cudaEventRecord(static_cast<cudaEvent_t>(a->event_main_begin), st);
   const dim3 grid(ceil_div(s.max_seqlen_k, nb::kTile), s.heads, s.batch);
   nb::attn_bwd_kernel<<<grid, nb::kBwdThreads, nb::kBwdSmemBytes, st>>>(tq, tk, tv, tg, p);
+  if (a->event_main_end) cudaEventRecord(static_cast<cudaEvent_t>(a->event_main_end), st);
   nb::attn_bwd_epilogue_kernel<<<aux_blocks, 256, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? NB_ATTN_OK : NB_ATTN_ERR_LAUNCH;
 }

@@ -79,7 +79,7 @@ def test_fwd_rejects_bad_arguments_without_a_gpu(lib):
 def test_bwd_rejects_bad_workspace_without_a_gpu(lib):
     ok = _tensor()
     need = lib.nb_attn_bwd_workspace_bytes(16, 2, 64)
-    mk = lambda ws, nbytes: _lib.BwdArgs(_shape(), ok, ok, ok, ok, ok, ok, ok, ok, 0x10000, ws, nbytes, None)
+    mk = lambda ws, nbytes: _lib.BwdArgs(_shape(), ok, ok, ok, ok, ok, ok, ok, ok, 0x10000, ws, nbytes, None, None, None)
     assert lib.nb_attn_bwd(C.byref(mk(None, need)), None) == 5
     assert lib.nb_attn_bwd(C.byref(mk(0x20000, need - 1)), None) == 5
     assert lib.nb_attn_bwd(C.byref(mk(0x20010, need)), None) == 5  # not 256-byte aligned
