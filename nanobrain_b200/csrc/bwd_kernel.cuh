@@ -4,7 +4,7 @@
 //                              clears the fp32 dQ accumulator. HBM-bound.
 //   attn_bwd_kernel          : one CTA owns one 128-row K/V tile of one (sequence, head) and walks
 //                              the sequence's queries in 128-row tiles. Everything is computed
-//                              transposed so that thread r owns key row r (tensor-memory lane r):
+//                              transposed so that a thread owns a key row (tensor-memory lane):
 //                                S^T  = K Q^T                       (tcgen05, smem x smem)
 //                                dP^T = V dO^T                      (tcgen05, smem x smem)
 //                                P^T  = exp2(S^T*scale_log2 - lse)  (recomputed from the saved LSE)
@@ -14,6 +14,13 @@
 //                                dQ   = dS K                        (same dS bytes read MN-major)
 //                              dQ tiles are added into the fp32 accumulator with vector atomics
 //                              because every K/V tile of a sequence contributes to every dQ row.
+//                              Warp roles (512 threads): warps 0-7 are two compute warpgroups that
+//                              split the 128 query columns of a tile (64 each); warps 8-11 are
+//                              four MMA issuers (S^T/dP^T, dV, dK, dQ: one elected thread each --
+//                              a single thread can issue a tcgen05.mma only every ~55 cycles, so
+//                              the 32 MMAs of a tile need several issuers to keep the tensor pipe
+//                              fed); warp 12 drives TMA and stages LSE/delta rows (warps 13-15 only complete its
+//                              warpgroup for the register re-partitioning).
 //   attn_bwd_epilogue_kernel : dQ = bf16(scale * accumulator). HBM-bound.
 #pragma once
 
@@ -112,22 +119,53 @@ __global__ void __launch_bounds__(256) attn_bwd_epilogue_kernel(const BwdParams 
 // ----------------------------------------------------------------------------------------
 // Main backward kernel
 // ----------------------------------------------------------------------------------------
-constexpr int kBwdThreads = 128;
-// K, V, 2x(Q, dO), dS (two 64-column halves) + LSE/delta stages + alignment slack
-constexpr int kBwdSmemBytes = 8 * kTileBytes + 2 * 2 * kTile * 4 + 1024;
+constexpr int kBwdThreads = 512;
+constexpr int kBwdStages = 3;  // Q/dO ring
+// K, V, 3x(Q, dO), 2 x dS (two 64-column halves each) + LSE/delta stages + alignment slack
+constexpr int kBwdSmemBytes = (2 + 2 * kBwdStages + 4) * kTileBytes + kBwdStages * 2 * kTile * 4 + 1024;
 constexpr int kBwdTmemCols = 512;  // S^T 0, dP^T 128, P^T 256, dV 320, dK 384, dQ 448
+// Register re-partitioning. The CTA launches with 512 threads x 128 registers (the whole register
+// file of the SM); setmaxnreg only moves registers inside that allocation, so the budget must
+// balance exactly or the growing warps would wait for ever:
+//   2 compute warpgroups x 128 threads x 208 + issuer warpgroup x 128 x 56 + TMA warpgroup x 128 x 40
+//   = 53248 + 7168 + 5120 = 65536 = 512 x 128.
+// Every warp of an aligned warpgroup executes the same setmaxnreg instruction (warps 13-15 exist
+// only to complete the TMA warp's warpgroup).
+constexpr int kBwdComputeRegs = 208;
+constexpr int kBwdIssuerRegs = 56;
+constexpr int kBwdLoaderRegs = 40;
+static_assert(256 * kBwdComputeRegs + 128 * kBwdIssuerRegs + 128 * kBwdLoaderRegs == 512 * 128, "register budget");
 
-__global__ void __launch_bounds__(kBwdThreads)
+enum BwdBar : int {
+  kBarKvFull = 0,
+  kBarQdoFull = 1,                       // [kBwdStages]
+  kBarQdoEmpty = kBarQdoFull + kBwdStages,  // [kBwdStages], 3 arrivals: S/dP, dV and dK issuers
+  kBarSFull = kBarQdoEmpty + kBwdStages,
+  kBarSFree,    // 8 arrivals (one per compute warp)
+  kBarDpFull,
+  kBarDpFree,   // 8
+  kBarPFull,    // 8
+  kBarPtFree,   // dV MMAs of the tile have consumed P^T
+  kBarDsFull,   // [2], 8 arrivals
+  kBarDsFree = kBarDsFull + 2,  // [2], 2 arrivals: dK and dQ issuers
+  kBarDqFull = kBarDsFree + 2,
+  kBarDqFree,   // 8
+  kBarDkDone,
+  kBwdNumBars
+};
+
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                 const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[6];  // kv, qdo0, qdo1, s, dp, dq
+  __shared__ __align__(8) uint64_t bars[kBwdNumBars];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int abort_flag;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
+  const int lane = tid & 31;
   const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
 
   int q_begin = 0, k_begin = 0, lq = p.lq, lk = p.lk, bcoord = b;
@@ -146,232 +184,351 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t smem_base = smem_u32(smem_al);
   const uint32_t sK = smem_base;
   const uint32_t sV = smem_base + 1 * kTileBytes;
-  const uint32_t sQ[2] = {smem_base + 2 * kTileBytes, smem_base + 4 * kTileBytes};
-  const uint32_t sDO[2] = {smem_base + 3 * kTileBytes, smem_base + 5 * kTileBytes};
-  const uint32_t sDS = smem_base + 6 * kTileBytes;  // 32 KB: q columns 0..63 | 64..127
-  uint8_t* sDS_ptr = smem_al + 6 * kTileBytes;
-  float* sLse = reinterpret_cast<float*>(smem_al + 8 * kTileBytes);  // [2][128], log2 domain
-  float* sDelta = sLse + 2 * kTile;                                  // [2][128]
+  auto sQ = [&](int s) { return smem_base + (2 + 2 * s) * kTileBytes; };
+  auto sDO = [&](int s) { return smem_base + (3 + 2 * s) * kTileBytes; };
+  constexpr int kDsTile0 = 2 + 2 * kBwdStages;
+  auto sDS = [&](int d) { return smem_base + (kDsTile0 + 2 * d) * kTileBytes; };  // 32 KB: q columns 0..63 | 64..127
+  uint8_t* sDS_ptr = smem_al + kDsTile0 * kTileBytes;
+  float* sLse = reinterpret_cast<float*>(smem_al + (kDsTile0 + 4) * kTileBytes);  // [stages][128], log2 domain
+  float* sDelta = sLse + kBwdStages * kTile;                                      // [stages][128]
 
-  const uint32_t bar_kv = smem_u32(&bars[0]);
-  const uint32_t bar_qdo[2] = {smem_u32(&bars[1]), smem_u32(&bars[2])};
-  const uint32_t bar_s = smem_u32(&bars[3]);
-  const uint32_t bar_dp = smem_u32(&bars[4]);
-  const uint32_t bar_dq = smem_u32(&bars[5]);
+  const uint32_t bar0 = smem_u32(&bars[0]);
+  auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
 
   if (tid == 0) {
     abort_flag = 0;
-    for (int i = 0; i < 6; ++i) mbar_init(smem_u32(&bars[i]), 1);
+    for (int i = 0; i < kBwdNumBars; ++i) {
+      uint32_t count = 1;
+      if (i >= kBarQdoEmpty && i < kBarQdoEmpty + kBwdStages) count = 3;
+      if (i == kBarSFree || i == kBarDpFree || i == kBarPFull || i == kBarDqFree) count = 8;
+      if (i == kBarDsFull || i == kBarDsFull + 1) count = 8;
+      if (i == kBarDsFree || i == kBarDsFree + 1) count = 2;
+      mbar_init(bar(i), count);
+    }
     fence_mbar_init();
-    tma_prefetch_desc(&tmap_q);
-    tma_prefetch_desc(&tmap_k);
-    tma_prefetch_desc(&tmap_v);
-    tma_prefetch_desc(&tmap_do);
   }
-  if (warp == 0) {
-    __syncwarp();
+  if (warp == 8) {
     tmem_alloc(smem_u32(&tmem_base_slot), kBwdTmemCols);
     tmem_relinquish();
   }
-
-  // LSE (converted to the log2 domain) and delta of query tile `jt` into stage `stg`. Rows past
-  // the end of the sequence get lse = +inf, which makes their P^T column exactly zero.
-  const int64_t stat_base = p.cu_q != nullptr ? int64_t(h) * p.total_q + q_begin : (int64_t(b) * p.heads + h) * p.lq;
-  auto load_stats = [&](int jt, int stg) {
-    const int r = jt * kTile + tid;
-    float l2 = INFINITY, dl = 0.f;
-    if (r < lq) {
-      l2 = p.lse[stat_base + r] * 1.4426950408889634f;
-      dl = p.delta[stat_base + r];
-    }
-    sLse[stg * kTile + tid] = l2;
-    sDelta[stg * kTile + tid] = dl;
-  };
-  if (n_q > 0) load_stats(0, 0);
-
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_slot;
   const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_pt = tmem_base + 256;
   const uint32_t tm_dv = tmem_base + 320, tm_dk = tmem_base + 384, tm_dq = tmem_base + 448;
-  const uint32_t lane_off = uint32_t(warp * 32) << 16;
 
-  constexpr uint32_t kIdescS = make_idesc(128, 128, 0, 0);     // K-major x K-major, N = 128
-  constexpr uint32_t kIdescKN = make_idesc(128, 64, 0, 1);     // A K-major / tensor memory, B MN-major
-  constexpr uint32_t kIdescNN = make_idesc(128, 64, 1, 1);     // A MN-major, B MN-major
-
-  auto issue_s_dp = [&](int stg) {
-    const uint64_t kd = make_sdesc(sK, 16, 1024), qd = make_sdesc(sQ[stg], 16, 1024);
-    const uint64_t vd = make_sdesc(sV, 16, 1024), gd = make_sdesc(sDO[stg], 16, 1024);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) mma_ss(tm_s, kd + 2 * k, qd + 2 * k, kIdescS, k > 0);
-    tc_commit(bar_s);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) mma_ss(tm_dp, vd + 2 * k, gd + 2 * k, kIdescS, k > 0);
-    tc_commit(bar_dp);
-  };
+  constexpr uint32_t kIdescS = make_idesc(128, 128, 0, 0);   // K-major x K-major, N = 128
+  constexpr uint32_t kIdescKN = make_idesc(128, 64, 0, 1);   // A K-major / tensor memory, B MN-major
+  constexpr uint32_t kIdescNN = make_idesc(128, 64, 1, 1);   // A MN-major, B MN-major
+  const int64_t stat_base = p.cu_q != nullptr ? int64_t(h) * p.total_q + q_begin : (int64_t(b) * p.heads + h) * p.lq;
 
   if (n_q > 0) {
-    if (tid == 0) {
-      mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
-      tma_load_4d(sK, &tmap_k, bar_kv, 0, k_begin + k_row0, h, bcoord);
-      tma_load_4d(sV, &tmap_v, bar_kv, 0, k_begin + k_row0, h, bcoord);
-      mbar_arrive_expect_tx(bar_qdo[0], 2 * kTileBytes);
-      tma_load_4d(sQ[0], &tmap_q, bar_qdo[0], 0, q_begin, h, bcoord);
-      tma_load_4d(sDO[0], &tmap_do, bar_qdo[0], 0, q_begin, h, bcoord);
-      mbar_wait(bar_kv, 0, &abort_flag, p.status);
-      mbar_wait(bar_qdo[0], 0, &abort_flag, p.status);
-      tc_fence_after();
-      issue_s_dp(0);
-    }
-    __syncwarp();
-
-    const bool row_valid = (k_row0 + tid) < lk;
-
-    for (int j = 0; j < n_q; ++j) {
-      const int st = j & 1;
-      if (j + 1 < n_q) {
-        if (tid == 0) {
-          mbar_arrive_expect_tx(bar_qdo[st ^ 1], 2 * kTileBytes);
-          tma_load_4d(sQ[st ^ 1], &tmap_q, bar_qdo[st ^ 1], 0, q_begin + (j + 1) * kTile, h, bcoord);
-          tma_load_4d(sDO[st ^ 1], &tmap_do, bar_qdo[st ^ 1], 0, q_begin + (j + 1) * kTile, h, bcoord);
+    if (warp >= 12) {
+      // ---------------- TMA producer + LSE/delta staging (warp 12; 13-15 idle) ----------------
+      setmaxnreg_dec<kBwdLoaderRegs>();
+      if (warp == 12) {
+      if (lane == 0) {
+        tma_prefetch_desc(&tmap_q);
+        tma_prefetch_desc(&tmap_k);
+        tma_prefetch_desc(&tmap_v);
+        tma_prefetch_desc(&tmap_do);
+        mbar_arrive_expect_tx(bar(kBarKvFull), 2 * kTileBytes);
+        tma_load_4d(sK, &tmap_k, bar(kBarKvFull), 0, k_begin + k_row0, h, bcoord);
+        tma_load_4d(sV, &tmap_v, bar(kBarKvFull), 0, k_begin + k_row0, h, bcoord);
+      }
+      for (int j = 0; j < n_q; ++j) {
+        const int qs = j % kBwdStages;
+        const int jt = (j + kt) % n_q;  // staggered start: concurrent CTAs touch different dQ tiles
+        if (j >= kBwdStages && lane == 0)
+          mbar_wait(bar(kBarQdoEmpty + qs), ((j / kBwdStages) - 1) & 1, &abort_flag, p.status);
+        __syncwarp();
+        // Staged negated: -lse in the log2 domain and -delta. Rows past the end of the sequence get
+        // -lse = -inf, which makes their P^T column exactly 0.
+#pragma unroll
+        for (int r4 = 0; r4 < 4; ++r4) {
+          const int r = jt * kTile + r4 * 32 + lane;
+          float l2 = -INFINITY, dl = 0.f;
+          if (r < lq) {
+            l2 = p.lse[stat_base + r] * -1.4426950408889634f;
+            dl = -p.delta[stat_base + r];
+          }
+          sLse[qs * kTile + r4 * 32 + lane] = l2;
+          sDelta[qs * kTile + r4 * 32 + lane] = dl;
         }
         __syncwarp();
-        load_stats(j + 1, st ^ 1);
-      }
-
-      mbar_wait(bar_s, j & 1, &abort_flag, p.status);
-      tc_fence_after();
-      const float* lse_s = sLse + st * kTile;
-      const float* dl_s = sDelta + st * kTile;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        float pf[32];
-        tmem_ld32(tm_s + lane_off + c * 32, r);
-        tmem_wait_ld();
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float pv = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -lse_s[c * 32 + i]));
-          pf[i] = row_valid ? pv : 0.f;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(bar(kBarQdoFull + qs), 2 * kTileBytes);
+          tma_load_4d(sQ(qs), &tmap_q, bar(kBarQdoFull + qs), 0, q_begin + jt * kTile, h, bcoord);
+          tma_load_4d(sDO(qs), &tmap_do, bar(kBarQdoFull + qs), 0, q_begin + jt * kTile, h, bcoord);
         }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(pf[2 * i], pf[2 * i + 1]);
-        tmem_st16(tm_pt + lane_off + c * 16, pk);
-
-        if (c == 0) {
-          mbar_wait(bar_dp, j & 1, &abort_flag, p.status);
+      }
+      }
+    } else if (warp >= 8) {
+      setmaxnreg_dec<kBwdIssuerRegs>();
+      if (warp == 8) {
+      // ---------------- MMA issuer: S^T = K Q^T and dP^T = V dO^T ----------------
+      if (elect_one()) {
+        const uint64_t kd = make_sdesc(sK, 16, 1024), vd = make_sdesc(sV, 16, 1024);
+        mbar_wait(bar(kBarKvFull), 0, &abort_flag, p.status);
+        for (int j = 0; j < n_q; ++j) {
+          const int qs = j % kBwdStages;
+          mbar_wait(bar(kBarQdoFull + qs), (j / kBwdStages) & 1, &abort_flag, p.status);
+          if (j > 0) mbar_wait(bar(kBarSFree), (j - 1) & 1, &abort_flag, p.status);
           tc_fence_after();
-        }
-        tmem_ld32(tm_dp + lane_off + c * 32, r);
-        tmem_wait_ld();
+          const uint64_t qd = make_sdesc(sQ(qs), 16, 1024), gd = make_sdesc(sDO(qs), 16, 1024);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float d0 = pf[2 * i] * (__uint_as_float(r[2 * i]) - dl_s[c * 32 + 2 * i]);
-          const float d1 = pf[2 * i + 1] * (__uint_as_float(r[2 * i + 1]) - dl_s[c * 32 + 2 * i + 1]);
-          pk[i] = pack_bf16(d0, d1);
-        }
-        // dS^T row `tid`, query columns [32c, 32c+32): four 16-byte chunks of the swizzled row.
-        uint8_t* half = sDS_ptr + (c >> 1) * kTileBytes;
+          for (int k = 0; k < 4; ++k) mma_ss(tm_s, kd + 2 * k, qd + 2 * k, kIdescS, k > 0);
+          tc_commit(bar(kBarSFull));
+          if (j > 0) mbar_wait(bar(kBarDpFree), (j - 1) & 1, &abort_flag, p.status);
+          tc_fence_after();
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const uint4 v = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
-          *reinterpret_cast<uint4*>(half + swz128(tid, (c & 1) * 4 + q4)) = v;
+          for (int k = 0; k < 4; ++k) mma_ss(tm_dp, vd + 2 * k, gd + 2 * k, kIdescS, k > 0);
+          tc_commit(bar(kBarDpFull));
+          tc_commit(bar(kBarQdoEmpty + qs));
         }
       }
-      tmem_wait_st();
-      fence_proxy_async_smem();
-      tc_fence_before();
-      __syncthreads();
-
-      if (tid == 0) {
-        tc_fence_after();
-        const uint64_t gd_mn = make_sdesc(sDO[st], 1024, 1024);
-        const uint64_t qd_mn = make_sdesc(sQ[st], 1024, 1024);
+      } else if (warp == 9) {
+      // ---------------- MMA issuer: dV += P^T dO ----------------
+      if (elect_one()) {
+        for (int j = 0; j < n_q; ++j) {
+          const int qs = j % kBwdStages;
+          mbar_wait(bar(kBarPFull), j & 1, &abort_flag, p.status);
+          mbar_wait(bar(kBarQdoFull + qs), (j / kBwdStages) & 1, &abort_flag, p.status);
+          tc_fence_after();
+          const uint64_t gd_mn = make_sdesc(sDO(qs), 1024, 1024);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) mma_ts(tm_dv, tm_pt + 8 * k, gd_mn + 128 * k, kIdescKN, (j > 0) || (k > 0));
+          tc_commit(bar(kBarPtFree));
+          tc_commit(bar(kBarQdoEmpty + qs));
+        }
+      }
+      } else if (warp == 10) {
+      // ---------------- MMA issuer: dK += dS^T Q ----------------
+      if (elect_one()) {
+        for (int j = 0; j < n_q; ++j) {
+          const int qs = j % kBwdStages, db = j & 1;
+          mbar_wait(bar(kBarDsFull + db), (j >> 1) & 1, &abort_flag, p.status);
+          mbar_wait(bar(kBarQdoFull + qs), (j / kBwdStages) & 1, &abort_flag, p.status);
+          tc_fence_after();
+          const uint64_t qd_mn = make_sdesc(sQ(qs), 1024, 1024);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            // A: K-major view of the dS buffer; one K step = 16 query columns.
+            const uint64_t ad = make_sdesc(sDS(db) + (k >> 2) * kTileBytes, 16, 1024) + 2 * (k & 3);
+            mma_ss(tm_dk, ad, qd_mn + 128 * k, kIdescKN, (j > 0) || (k > 0));
+          }
+          tc_commit(bar(kBarDsFree + db));
+          tc_commit(bar(kBarQdoEmpty + qs));
+        }
+        tc_commit(bar(kBarDkDone));
+      }
+      } else {
+      // ---------------- MMA issuer: dQ = dS K ----------------
+      if (elect_one()) {
         const uint64_t kd_mn = make_sdesc(sK, 1024, 1024);
-        const uint64_t ds_mn = make_sdesc(sDS, kTileBytes, 1024);
-        // dV += P^T dO
-#pragma unroll
-        for (int k = 0; k < 8; ++k) mma_ts(tm_dv, tm_pt + 8 * k, gd_mn + 128 * k, kIdescKN, (j > 0) || (k > 0));
-        // dK += dS^T Q   (A: K-major view of the dS buffer; K step = 16 query columns)
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint64_t ad = make_sdesc(sDS + (k >> 2) * kTileBytes, 16, 1024) + 2 * (k & 3);
-          mma_ss(tm_dk, ad, qd_mn + 128 * k, kIdescKN, (j > 0) || (k > 0));
-        }
-        // dQ = dS K      (A: MN-major view of the same bytes; K step = 16 key rows)
-#pragma unroll
-        for (int k = 0; k < 8; ++k) mma_ss(tm_dq, ds_mn + 128 * k, kd_mn + 128 * k, kIdescNN, k > 0);
-        tc_commit(bar_dq);
-        if (j + 1 < n_q) {
-          mbar_wait(bar_qdo[st ^ 1], ((j + 1) >> 1) & 1, &abort_flag, p.status);
+        mbar_wait(bar(kBarKvFull), 0, &abort_flag, p.status);
+        for (int j = 0; j < n_q; ++j) {
+          const int db = j & 1;
+          mbar_wait(bar(kBarDsFull + db), (j >> 1) & 1, &abort_flag, p.status);
+          if (j > 0) mbar_wait(bar(kBarDqFree), (j - 1) & 1, &abort_flag, p.status);
           tc_fence_after();
-          issue_s_dp(st ^ 1);
+          // A: MN-major view of the same dS bytes; one K step = 16 key rows.
+          const uint64_t ds_mn = make_sdesc(sDS(db), kTileBytes, 1024);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) mma_ss(tm_dq, ds_mn + 128 * k, kd_mn + 128 * k, kIdescNN, k > 0);
+          tc_commit(bar(kBarDqFull));
+          tc_commit(bar(kBarDsFree + db));
         }
       }
-      __syncwarp();
+      }
+    } else {
+      // ---------------- compute warpgroups: w = 0 / 1 owns query columns [64w, 64w+64) ----------------
+      setmaxnreg_inc<kBwdComputeRegs>();
+      const int w = warp >> 2;
+      const int krow_in_tile = tid & 127;  // key row of this thread = tensor-memory lane
+      const uint32_t lane_off = uint32_t((warp & 3) * 32) << 16;
+      const bool row_valid = (k_row0 + krow_in_tile) < lk;
+      const bool partial = (k_row0 + kTile) > lk;
+      const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
+      const int64_t acc_batch_row = int64_t(p.cu_q != nullptr ? 0 : b) * p.lq + q_begin;
 
-      // dQ tile -> fp32 accumulator. Here thread r owns QUERY row r of tile j.
-      mbar_wait(bar_dq, j & 1, &abort_flag, p.status);
+      // dQ tile (32 columns of this warpgroup) -> fp32 accumulator. The 16x256b fragments put 32
+      // contiguous bytes of a row into four neighbouring threads, so every warp-wide red.v2 adds
+      // whole 32-byte sectors.
+      auto reduce_dq = [&](int tile, const uint32_t (&r0)[16], const uint32_t (&r1)[16]) {
+        const int row_a = tile * kTile + (warp & 3) * 32 + (lane >> 2);
+        const int col = 32 * w + 2 * (lane & 3);
+#pragma unroll
+        for (int half16 = 0; half16 < 2; ++half16) {
+          const uint32_t(&r)[16] = half16 ? r1 : r0;
+#pragma unroll
+          for (int sub = 0; sub < 2; ++sub) {
+            const int qrow = row_a + 16 * half16 + 8 * sub;
+            if (qrow < lq) {
+              float* acc_row = p.dq_accum + ((acc_batch_row + qrow) * p.heads + h) * kHeadDim + col;
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                red_add_v2(acc_row + 8 * i, __uint_as_float(r[4 * i + 2 * sub]), __uint_as_float(r[4 * i + 2 * sub + 1]));
+            }
+          }
+        }
+      };
+
+      for (int j = 0; j < n_q; ++j) {
+        const int qs = j % kBwdStages, db = j & 1;
+        const float4* lse4 = reinterpret_cast<const float4*>(sLse + qs * kTile + 64 * w);   // -lse (log2)
+        const float4* dl4 = reinterpret_cast<const float4*>(sDelta + qs * kTile + 64 * w);  // -delta
+        uint64_t pf[32];  // P^T values of this thread as packed fp32 pairs
+
+        // ---- phase A: P^T = exp2(S^T * scale_log2 - lse) ----
+        mbar_wait2(bar(kBarQdoFull + qs), (j / kBwdStages) & 1, bar(kBarSFull), j & 1, &abort_flag, p.status);
+        tc_fence_after();
+        {
+          uint32_t ra[32], rb[32];
+          tmem_ld32(tm_s + lane_off + 64 * w, ra);
+          tmem_ld32(tm_s + lane_off + 64 * w + 32, rb);
+          tmem_wait_ld();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(kBarSFree));
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const uint32_t* src = i < 8 ? &ra[4 * i] : &rb[4 * (i - 8)];
+            const float4 l = lse4[i];
+            float x0, x1, x2, x3;
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(src[0]), __uint_as_float(src[1])), scale2,
+                                   pack_f32x2(l.x, l.y)), x0, x1);
+            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(src[2]), __uint_as_float(src[3])), scale2,
+                                   pack_f32x2(l.z, l.w)), x2, x3);
+            pf[2 * i] = pack_f32x2(fast_exp2(x0), fast_exp2(x1));
+            pf[2 * i + 1] = pack_f32x2(fast_exp2(x2), fast_exp2(x3));
+          }
+        }
+        if (partial && !row_valid) {
+          // Key rows past the end of the sequence must not contribute to dQ.
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pf[i] = 0ull;
+        }
+        if (j > 0) {
+          mbar_wait(bar(kBarPtFree), (j - 1) & 1, &abort_flag, p.status);
+          tc_fence_after();
+        }
+        {
+          uint32_t pk[16];
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float a0, a1;
+              unpack_f32x2(pf[16 * c + i], a0, a1);
+              pk[i] = pack_bf16(a0, a1);
+            }
+            tmem_st16(tm_pt + lane_off + 32 * w + 16 * c, pk);
+          }
+        }
+
+        // ---- middle: pull dQ of the previous tile and dP^T of this tile out of tensor memory ----
+        uint32_t q0[16], q1[16], ra[32], rb[32];
+        if (j > 0) {
+          mbar_wait2(bar(kBarDqFull), (j - 1) & 1, bar(kBarDpFull), j & 1, &abort_flag, p.status);
+          tc_fence_after();
+          tmem_ld_16x256b_x4(tm_dq + lane_off + 32 * w, q0);
+          tmem_ld_16x256b_x4(tm_dq + lane_off + (16u << 16) + 32 * w, q1);
+        } else {
+          mbar_wait(bar(kBarDpFull), j & 1, &abort_flag, p.status);
+          tc_fence_after();
+        }
+        tmem_ld32(tm_dp + lane_off + 64 * w, ra);
+        tmem_ld32(tm_dp + lane_off + 64 * w + 32, rb);
+        tmem_wait_ld();
+        tmem_wait_st();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bar(kBarPFull));
+          if (j > 0) mbar_arrive(bar(kBarDqFree));
+          mbar_arrive(bar(kBarDpFree));
+        }
+        if (j > 0) reduce_dq((j - 1 + kt) % n_q, q0, q1);
+
+        // ---- phase B: dS^T = P^T o (dP^T - delta) -> shared memory ----
+        if (j >= 2) mbar_wait(bar(kBarDsFree + db), ((j >> 1) - 1) & 1, &abort_flag, p.status);
+        uint8_t* half = sDS_ptr + (2 * db + w) * kTileBytes;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = query columns [8c, 8c+8) of this half
+          const uint32_t* src = c < 4 ? &ra[8 * c] : &rb[8 * (c - 4)];
+          const float4 d0 = dl4[2 * c], d1 = dl4[2 * c + 1];
+          const uint64_t nd[4] = {pack_f32x2(d0.x, d0.y), pack_f32x2(d0.z, d0.w), pack_f32x2(d1.x, d1.y),
+                                  pack_f32x2(d1.z, d1.w)};
+          uint32_t o[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const uint64_t dp2 = pack_f32x2(__uint_as_float(src[2 * i]), __uint_as_float(src[2 * i + 1]));
+            float a0, a1;
+            unpack_f32x2(mul_f32x2(pf[4 * c + i], add_f32x2(dp2, nd[i])), a0, a1);
+            o[i] = pack_bf16(a0, a1);
+          }
+          *reinterpret_cast<uint4*>(half + swz128(krow_in_tile, c)) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(kBarDsFull + db));
+      }
+      {
+        // dQ of the last query tile.
+        uint32_t q0[16], q1[16];
+        mbar_wait(bar(kBarDqFull), (n_q - 1) & 1, &abort_flag, p.status);
+        tc_fence_after();
+        tmem_ld_16x256b_x4(tm_dq + lane_off + 32 * w, q0);
+        tmem_ld_16x256b_x4(tm_dq + lane_off + (16u << 16) + 32 * w, q1);
+        tmem_wait_ld();
+        reduce_dq((n_q - 1 + kt) % n_q, q0, q1);
+      }
+
+      // ---- epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK (scaled) ----
+      if (w == 0) mbar_wait(bar(kBarPtFree), (n_q - 1) & 1, &abort_flag, p.status);
+      else mbar_wait(bar(kBarDkDone), 0, &abort_flag, p.status);
       tc_fence_after();
-      const int qrow = j * kTile + tid;
-      float* acc_row = p.dq_accum + ((int64_t(p.cu_q != nullptr ? 0 : b) * p.lq + q_begin + qrow) * p.heads + h) * kHeadDim;
+      const int krow = k_row0 + krow_in_tile;
+      __nv_bfloat16* out_ptr =
+          w == 0 ? p.dv + int64_t(bcoord) * p.dv_sb + int64_t(k_begin + krow) * p.dv_st + int64_t(h) * p.dv_sh
+                 : p.dk + int64_t(bcoord) * p.dk_sb + int64_t(k_begin + krow) * p.dk_st + int64_t(h) * p.dk_sh;
+      const float out_scale = w == 0 ? 1.f : p.scale;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
-        tmem_ld32(tm_dq + lane_off + c * 32, r);
+        tmem_ld32((w == 0 ? tm_dv : tm_dk) + lane_off + c * 32, r);
         tmem_wait_ld();
-        if (qrow < lq) {
+        if (krow < lk) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float4 v = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                         __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-            atomicAdd(reinterpret_cast<float4*>(acc_row + c * 32 + 4 * i), v);
+          for (int i = 0; i < 4; ++i) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[8 * i + 0]) * out_scale, __uint_as_float(r[8 * i + 1]) * out_scale);
+            v.y = pack_bf16(__uint_as_float(r[8 * i + 2]) * out_scale, __uint_as_float(r[8 * i + 3]) * out_scale);
+            v.z = pack_bf16(__uint_as_float(r[8 * i + 4]) * out_scale, __uint_as_float(r[8 * i + 5]) * out_scale);
+            v.w = pack_bf16(__uint_as_float(r[8 * i + 6]) * out_scale, __uint_as_float(r[8 * i + 7]) * out_scale);
+            reinterpret_cast<uint4*>(out_ptr)[c * 4 + i] = v;
           }
         }
       }
-      tc_fence_before();
     }
-  }
-
-  // Epilogue: dK (scaled) and dV rows of this tile.
-  const int krow = k_row0 + tid;
-  __nv_bfloat16* dk_ptr = p.dk + int64_t(bcoord) * p.dk_sb + int64_t(k_begin + krow) * p.dk_st + int64_t(h) * p.dk_sh;
-  __nv_bfloat16* dv_ptr = p.dv + int64_t(bcoord) * p.dv_sb + int64_t(k_begin + krow) * p.dv_st + int64_t(h) * p.dv_sh;
-#pragma unroll
-  for (int c = 0; c < 2; ++c) {
-    uint32_t rk[32], rv[32];
-    if (n_q > 0) {
-      tmem_ld32(tm_dk + lane_off + c * 32, rk);
-      tmem_ld32(tm_dv + lane_off + c * 32, rv);
-      tmem_wait_ld();
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) rk[i] = rv[i] = 0u;
-    }
+  } else if (warp < 8) {
+    // No queries at all: dK = dV = 0.
+    const int w = warp >> 2;
+    const int krow = k_row0 + (tid & 127);
     if (krow < lk) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint4 a, g;
-        a.x = pack_bf16(__uint_as_float(rk[8 * i + 0]) * p.scale, __uint_as_float(rk[8 * i + 1]) * p.scale);
-        a.y = pack_bf16(__uint_as_float(rk[8 * i + 2]) * p.scale, __uint_as_float(rk[8 * i + 3]) * p.scale);
-        a.z = pack_bf16(__uint_as_float(rk[8 * i + 4]) * p.scale, __uint_as_float(rk[8 * i + 5]) * p.scale);
-        a.w = pack_bf16(__uint_as_float(rk[8 * i + 6]) * p.scale, __uint_as_float(rk[8 * i + 7]) * p.scale);
-        g.x = pack_bf16(__uint_as_float(rv[8 * i + 0]), __uint_as_float(rv[8 * i + 1]));
-        g.y = pack_bf16(__uint_as_float(rv[8 * i + 2]), __uint_as_float(rv[8 * i + 3]));
-        g.z = pack_bf16(__uint_as_float(rv[8 * i + 4]), __uint_as_float(rv[8 * i + 5]));
-        g.w = pack_bf16(__uint_as_float(rv[8 * i + 6]), __uint_as_float(rv[8 * i + 7]));
-        reinterpret_cast<uint4*>(dk_ptr)[c * 4 + i] = a;
-        reinterpret_cast<uint4*>(dv_ptr)[c * 4 + i] = g;
-      }
+      __nv_bfloat16* out_ptr =
+          w == 0 ? p.dv + int64_t(bcoord) * p.dv_sb + int64_t(k_begin + krow) * p.dv_st + int64_t(h) * p.dv_sh
+                 : p.dk + int64_t(bcoord) * p.dk_sb + int64_t(k_begin + krow) * p.dk_st + int64_t(h) * p.dk_sh;
+      for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(out_ptr)[c] = make_uint4(0, 0, 0, 0);
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) {
+  if (warp == 8) {
+    __syncwarp();
     tc_fence_after();
     tmem_dealloc(tmem_base, kBwdTmemCols);
   }

@@ -212,6 +212,46 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
       : "memory");
 }
 
+// 16 lanes x 256 bit, repeated 4 times along columns (32 columns): thread t of the warp receives,
+// for column block i (8 columns each), r[4i+0..1] = row (lane_base + t/4), columns 8i + 2(t%4) + {0,1}
+// and r[4i+2..3] = row (lane_base + 8 + t/4), same columns. Four neighbouring threads thus hold
+// 32 contiguous bytes of one row, which makes a warp-wide vector store or reduction hit whole
+// 32-byte sectors.
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+// Fire-and-forget fp32 vector reduction into global memory (two adjacent floats).
+__device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
+}
+
+// Register re-partitioning between warpgroups (all four warps of an aligned warpgroup execute it).
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
+// Waits for two barriers with the two polls in flight together (their latencies overlap).
+__device__ __forceinline__ void mbar_wait2(uint32_t bar_a, uint32_t par_a, uint32_t bar_b, uint32_t par_b,
+                                           volatile int* abort_flag, int* status_word) {
+  const bool a = mbar_try_wait(bar_a, par_a);
+  const bool b = mbar_try_wait(bar_b, par_b);
+  if (!a) mbar_wait(bar_a, par_a, abort_flag, status_word);
+  if (!b) mbar_wait(bar_b, par_b, abort_flag, status_word);
+}
+
 // ----------------------------------------------------------------------------------------
 // tcgen05.mma descriptors (bf16 inputs, fp32 accumulate, cta_group::1)
 // ----------------------------------------------------------------------------------------
