@@ -12,7 +12,7 @@
 //                                dV  += P^T dO                      (A = P^T from tensor memory)
 //                                dK  += dS^T Q                      (A = dS^T from shared memory)
 //                                dQ   = dS K                        (same dS bytes read MN-major)
-//                              dQ tiles are added into the fp32 accumulator with vector atomics
+//                              dQ tiles are added into the fp32 accumulator with TMA add-reductions
 //                              because every K/V tile of a sequence contributes to every dQ row.
 //                              Warp roles (512 threads): warps 0-7 are two compute warpgroups that
 //                              split the 128 query columns of a tile (64 each); warps 8-11 are
@@ -121,7 +121,8 @@ __global__ void __launch_bounds__(256) attn_bwd_epilogue_kernel(const BwdParams 
 // ----------------------------------------------------------------------------------------
 constexpr int kBwdThreads = 512;
 constexpr int kBwdStages = 3;  // Q/dO ring
-// K, V, 3x(Q, dO), 2 x dS (two 64-column halves each) + LSE/delta stages + alignment slack
+// K, V, 3x(Q, dO), dS (two 64-column halves), fp32 dQ staging (two 32-column halves) + LSE/delta
+// stages + alignment slack
 constexpr int kBwdSmemBytes = (2 + 2 * kBwdStages + 4) * kTileBytes + kBwdStages * 2 * kTile * 4 + 1024;
 constexpr int kBwdTmemCols = 512;  // S^T 0, dP^T 128, P^T 256, dV 320, dK 384, dQ 448
 // Register re-partitioning. The CTA launches with 512 threads x 128 registers (the whole register
@@ -146,9 +147,9 @@ enum BwdBar : int {
   kBarDpFree,   // 8
   kBarPFull,    // 8
   kBarPtFree,   // dV MMAs of the tile have consumed P^T
-  kBarDsFull,   // [2], 8 arrivals
-  kBarDsFree = kBarDsFull + 2,  // [2], 2 arrivals: dK and dQ issuers
-  kBarDqFull = kBarDsFree + 2,
+  kBarDsFull,   // 8 arrivals
+  kBarDsFree,   // 2 arrivals: dK and dQ issuers
+  kBarDqFull,
   kBarDqFree,   // 8
   kBarDkDone,
   kBwdNumBars
@@ -157,7 +158,7 @@ enum BwdBar : int {
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                 const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                const BwdParams p) {
+                const __grid_constant__ CUtensorMap tmap_dq, const BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t bars[kBwdNumBars];
   __shared__ uint32_t tmem_base_slot;
@@ -187,8 +188,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   auto sQ = [&](int s) { return smem_base + (2 + 2 * s) * kTileBytes; };
   auto sDO = [&](int s) { return smem_base + (3 + 2 * s) * kTileBytes; };
   constexpr int kDsTile0 = 2 + 2 * kBwdStages;
-  auto sDS = [&](int d) { return smem_base + (kDsTile0 + 2 * d) * kTileBytes; };  // 32 KB: q columns 0..63 | 64..127
+  const uint32_t sDS = smem_base + kDsTile0 * kTileBytes;  // 32 KB bf16: q columns 0..63 | 64..127
   uint8_t* sDS_ptr = smem_al + kDsTile0 * kTileBytes;
+  uint8_t* sDQ_ptr = smem_al + (kDsTile0 + 2) * kTileBytes;  // 32 KB fp32: d columns 0..31 | 32..63
   float* sLse = reinterpret_cast<float*>(smem_al + (kDsTile0 + 4) * kTileBytes);  // [stages][128], log2 domain
   float* sDelta = sLse + kBwdStages * kTile;                                      // [stages][128]
 
@@ -201,8 +203,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t count = 1;
       if (i >= kBarQdoEmpty && i < kBarQdoEmpty + kBwdStages) count = 3;
       if (i == kBarSFree || i == kBarDpFree || i == kBarPFull || i == kBarDqFree) count = 8;
-      if (i == kBarDsFull || i == kBarDsFull + 1) count = 8;
-      if (i == kBarDsFree || i == kBarDsFree + 1) count = 2;
+      if (i == kBarDsFull) count = 8;
+      if (i == kBarDsFree) count = 2;
       mbar_init(bar(i), count);
     }
     fence_mbar_init();
@@ -307,18 +309,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // ---------------- MMA issuer: dK += dS^T Q ----------------
       if (elect_one()) {
         for (int j = 0; j < n_q; ++j) {
-          const int qs = j % kBwdStages, db = j & 1;
-          mbar_wait(bar(kBarDsFull + db), (j >> 1) & 1, &abort_flag, p.status);
+          const int qs = j % kBwdStages;
+          mbar_wait(bar(kBarDsFull), j & 1, &abort_flag, p.status);
           mbar_wait(bar(kBarQdoFull + qs), (j / kBwdStages) & 1, &abort_flag, p.status);
           tc_fence_after();
           const uint64_t qd_mn = make_sdesc(sQ(qs), 1024, 1024);
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             // A: K-major view of the dS buffer; one K step = 16 query columns.
-            const uint64_t ad = make_sdesc(sDS(db) + (k >> 2) * kTileBytes, 16, 1024) + 2 * (k & 3);
+            const uint64_t ad = make_sdesc(sDS + (k >> 2) * kTileBytes, 16, 1024) + 2 * (k & 3);
             mma_ss(tm_dk, ad, qd_mn + 128 * k, kIdescKN, (j > 0) || (k > 0));
           }
-          tc_commit(bar(kBarDsFree + db));
+          tc_commit(bar(kBarDsFree));
           tc_commit(bar(kBarQdoEmpty + qs));
         }
         tc_commit(bar(kBarDkDone));
@@ -329,16 +331,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const uint64_t kd_mn = make_sdesc(sK, 1024, 1024);
         mbar_wait(bar(kBarKvFull), 0, &abort_flag, p.status);
         for (int j = 0; j < n_q; ++j) {
-          const int db = j & 1;
-          mbar_wait(bar(kBarDsFull + db), (j >> 1) & 1, &abort_flag, p.status);
+          mbar_wait(bar(kBarDsFull), j & 1, &abort_flag, p.status);
           if (j > 0) mbar_wait(bar(kBarDqFree), (j - 1) & 1, &abort_flag, p.status);
           tc_fence_after();
           // A: MN-major view of the same dS bytes; one K step = 16 key rows.
-          const uint64_t ds_mn = make_sdesc(sDS(db), kTileBytes, 1024);
+          const uint64_t ds_mn = make_sdesc(sDS, kTileBytes, 1024);
 #pragma unroll
           for (int k = 0; k < 8; ++k) mma_ss(tm_dq, ds_mn + 128 * k, kd_mn + 128 * k, kIdescNN, k > 0);
           tc_commit(bar(kBarDqFull));
-          tc_commit(bar(kBarDsFree + db));
+          tc_commit(bar(kBarDsFree));
         }
       }
       }
@@ -353,30 +354,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
       const int64_t acc_batch_row = int64_t(p.cu_q != nullptr ? 0 : b) * p.lq + q_begin;
 
-      // dQ tile (32 columns of this warpgroup) -> fp32 accumulator. The 16x256b fragments put 32
-      // contiguous bytes of a row into four neighbouring threads, so every warp-wide red.v2 adds
-      // whole 32-byte sectors.
-      auto reduce_dq = [&](int tile, const uint32_t (&r0)[16], const uint32_t (&r1)[16]) {
-        const int row_a = tile * kTile + (warp & 3) * 32 + (lane >> 2);
-        const int col = 32 * w + 2 * (lane & 3);
+      // dQ tile -> fp32 accumulator. Each warp stages its 32 rows x 32 columns (fp32, 128-byte
+      // swizzled rows) in shared memory and one lane issues a TMA add-reduction for that 4 KB box,
+      // so only warp-level synchronisation is needed and L2 receives whole 128-byte lines. Rows past
+      // the end of the sequence hold exact zeros (their P^T column is 0), so adding them is harmless.
+      uint8_t* dq_stage = sDQ_ptr + w * kTileBytes + (warp & 3) * 4096;
+      auto reduce_dq = [&](int tile, const uint32_t (&r)[32]) {
+        if (lane == 0) bulk_wait_group_read0();  // the previous reduction has read the staging rows
+        __syncwarp();
 #pragma unroll
-        for (int half16 = 0; half16 < 2; ++half16) {
-          const uint32_t(&r)[16] = half16 ? r1 : r0;
-#pragma unroll
-          for (int sub = 0; sub < 2; ++sub) {
-            const int qrow = row_a + 16 * half16 + 8 * sub;
-            if (qrow < lq) {
-              float* acc_row = p.dq_accum + ((acc_batch_row + qrow) * p.heads + h) * kHeadDim + col;
-#pragma unroll
-              for (int i = 0; i < 4; ++i)
-                red_add_v2(acc_row + 8 * i, __uint_as_float(r[4 * i + 2 * sub]), __uint_as_float(r[4 * i + 2 * sub + 1]));
-            }
-          }
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(dq_stage + swz128(lane, c)) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_3d(&tmap_dq, smem_u32(dq_stage), 32 * w, int(acc_batch_row) + tile * kTile + (warp & 3) * 32, h);
+          bulk_commit_group();
         }
       };
 
       for (int j = 0; j < n_q; ++j) {
-        const int qs = j % kBwdStages, db = j & 1;
+        const int qs = j % kBwdStages;
         const float4* lse4 = reinterpret_cast<const float4*>(sLse + qs * kTile + 64 * w);   // -lse (log2)
         const float4* dl4 = reinterpret_cast<const float4*>(sDelta + qs * kTile + 64 * w);  // -delta
         uint64_t pf[32];  // P^T values of this thread as packed fp32 pairs
@@ -429,12 +427,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
 
         // ---- middle: pull dQ of the previous tile and dP^T of this tile out of tensor memory ----
-        uint32_t q0[16], q1[16], ra[32], rb[32];
+        uint32_t rq[32], ra[32], rb[32];
         if (j > 0) {
           mbar_wait2(bar(kBarDqFull), (j - 1) & 1, bar(kBarDpFull), j & 1, &abort_flag, p.status);
           tc_fence_after();
-          tmem_ld_16x256b_x4(tm_dq + lane_off + 32 * w, q0);
-          tmem_ld_16x256b_x4(tm_dq + lane_off + (16u << 16) + 32 * w, q1);
+          tmem_ld32(tm_dq + lane_off + 32 * w, rq);
         } else {
           mbar_wait(bar(kBarDpFull), j & 1, &abort_flag, p.status);
           tc_fence_after();
@@ -450,11 +447,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           if (j > 0) mbar_arrive(bar(kBarDqFree));
           mbar_arrive(bar(kBarDpFree));
         }
-        if (j > 0) reduce_dq((j - 1 + kt) % n_q, q0, q1);
+        if (j > 0) reduce_dq((j - 1 + kt) % n_q, rq);
 
         // ---- phase B: dS^T = P^T o (dP^T - delta) -> shared memory ----
-        if (j >= 2) mbar_wait(bar(kBarDsFree + db), ((j >> 1) - 1) & 1, &abort_flag, p.status);
-        uint8_t* half = sDS_ptr + (2 * db + w) * kTileBytes;
+        if (j > 0) mbar_wait(bar(kBarDsFree), (j - 1) & 1, &abort_flag, p.status);
+        uint8_t* half = sDS_ptr + w * kTileBytes;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = query columns [8c, 8c+8) of this half
           const uint32_t* src = c < 4 ? &ra[8 * c] : &rb[8 * (c - 4)];
@@ -473,17 +470,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(kBarDsFull + db));
+        if (lane == 0) mbar_arrive(bar(kBarDsFull));
       }
       {
         // dQ of the last query tile.
-        uint32_t q0[16], q1[16];
+        uint32_t rq[32];
         mbar_wait(bar(kBarDqFull), (n_q - 1) & 1, &abort_flag, p.status);
         tc_fence_after();
-        tmem_ld_16x256b_x4(tm_dq + lane_off + 32 * w, q0);
-        tmem_ld_16x256b_x4(tm_dq + lane_off + (16u << 16) + 32 * w, q1);
+        tmem_ld32(tm_dq + lane_off + 32 * w, rq);
         tmem_wait_ld();
-        reduce_dq((n_q - 1 + kt) % n_q, q0, q1);
+        reduce_dq((n_q - 1 + kt) % n_q, rq);
+        if (lane == 0) bulk_wait_group0();  // all reductions of this warp have landed
       }
 
       // ---- epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK (scaled) ----

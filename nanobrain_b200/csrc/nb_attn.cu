@@ -110,6 +110,21 @@ int make_tmap(CUtensorMap* map, const nb_attn_tensor& t, const nb_attn_shape& s,
   return r == CUDA_SUCCESS ? NB_ATTN_OK : NB_ATTN_ERR_TENSOR_MAP;
 }
 
+// 3-D fp32 map over the dQ accumulator [token][head][64]: (64, tokens, heads), box 32 x 32 x 1 with
+// 128-byte swizzle, used by the backward kernel's TMA add-reductions.
+int make_dq_accum_tmap(CUtensorMap* map, float* accum, int64_t total_q, int heads) {
+  EncodeTiledFn enc = get_encode();
+  if (enc == nullptr) return NB_ATTN_ERR_TENSOR_MAP;
+  cuuint64_t dims[3] = {uint64_t(nb::kHeadDim), uint64_t(total_q), uint64_t(heads)};
+  cuuint64_t strides[2] = {uint64_t(heads) * nb::kHeadDim * sizeof(float), uint64_t(nb::kHeadDim) * sizeof(float)};
+  cuuint32_t box[3] = {32u, 32u, 1u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, accum, dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? NB_ATTN_OK : NB_ATTN_ERR_TENSOR_MAP;
+}
+
 constexpr float kLog2e = 1.4426950408889634f;
 
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
@@ -194,9 +209,10 @@ int nb_attn_bwd(const nb_attn_bwd_args* a, void* stream) {
     return NB_ATTN_ERR_WORKSPACE;
   if ((rc = ensure_device_ready())) return rc;
 
-  CUtensorMap tq, tk, tv, tg;
+  CUtensorMap tq, tk, tv, tg, tdq;
   if ((rc = make_tmap(&tq, a->q, s, true)) || (rc = make_tmap(&tk, a->k, s, false)) ||
-      (rc = make_tmap(&tv, a->v, s, false)) || (rc = make_tmap(&tg, a->d_o, s, true)))
+      (rc = make_tmap(&tv, a->v, s, false)) || (rc = make_tmap(&tg, a->d_o, s, true)) ||
+      (rc = make_dq_accum_tmap(&tdq, static_cast<float*>(a->workspace), s.total_q, s.heads)))
     return rc;
 
   nb::BwdParams p;
@@ -241,7 +257,7 @@ int nb_attn_bwd(const nb_attn_bwd_args* a, void* stream) {
   nb::attn_bwd_prologue_kernel<<<aux_blocks, 256, 0, st>>>(p);
   if (a->event_main_begin) cudaEventRecord(static_cast<cudaEvent_t>(a->event_main_begin), st);
   const dim3 grid(ceil_div(s.max_seqlen_k, nb::kTile), s.heads, s.batch);
-  nb::attn_bwd_kernel<<<grid, nb::kBwdThreads, nb::kBwdSmemBytes, st>>>(tq, tk, tv, tg, p);
+  nb::attn_bwd_kernel<<<grid, nb::kBwdThreads, nb::kBwdSmemBytes, st>>>(tq, tk, tv, tg, tdq, p);
   if (a->event_main_end) cudaEventRecord(static_cast<cudaEvent_t>(a->event_main_end), st);
   nb::attn_bwd_epilogue_kernel<<<aux_blocks, 256, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? NB_ATTN_OK : NB_ATTN_ERR_LAUNCH;
