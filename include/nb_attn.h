@@ -49,7 +49,8 @@ enum nb_attn_error {
   NB_ATTN_ERR_WORKSPACE = 5,   /* workspace missing or too small */
   NB_ATTN_ERR_TENSOR_MAP = 6,  /* the driver rejected a TMA tensor map */
   NB_ATTN_ERR_LAUNCH = 7,      /* a CUDA runtime call failed */
-  NB_ATTN_ERR_DEVICE = 8       /* the current device is not sm_100 */
+  NB_ATTN_ERR_DEVICE = 8,      /* the current device is not sm_100 */
+  NB_ATTN_ERR_TOO_LARGE = 9    /* problem exceeds the built-in scratch of nb_attn_bwd_builtin_scratch */
 };
 
 typedef struct nb_attn_tensor {
@@ -108,6 +109,30 @@ int nb_attn_bwd(const nb_attn_bwd_args* args, void* stream);
 /* Scratch bytes nb_attn_bwd needs: an fp32 dQ accumulator [total_q][heads][64] plus the
  * per-row dO.O dot products [heads * total_q]. */
 size_t nb_attn_bwd_workspace_bytes(int64_t total_q, int32_t heads, int32_t head_dim);
+
+/* Backward for callers that cannot allocate device memory (no counterpart in the reference).
+ *
+ * Who needs it: code that runs where a device allocation is forbidden or unavailable -- inside a
+ * region that must not touch the allocator (for example between two phases of a memory-planned
+ * training step whose pool is fully committed), in a host process that only borrows device
+ * pointers from another runtime and owns no allocator of its own, or in a latency-critical loop
+ * where a cudaMalloc would serialise the device. Such a caller still passes every input and output
+ * buffer, but not the scratch: this entry point ignores args->workspace / workspace_bytes and uses
+ * a fixed array that lives inside the library image on each GPU (NB_ATTN_BUILTIN_SCRATCH_ROWS rows
+ * of 260 bytes, about 16.3 MiB per GPU that loads the library, held until the process exits).
+ *
+ * Limits and rules
+ *  - total_q * heads must not exceed NB_ATTN_BUILTIN_SCRATCH_ROWS; larger problems are refused
+ *    with NB_ATTN_ERR_TOO_LARGE and nothing is launched. Use nb_attn_bwd with your own workspace.
+ *  - The call performs no cudaMalloc / cudaFree and calls no allocating library routine.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress with
+ *    that device current). Make that first call outside any CUDA stream capture.
+ *  - All calls on a GPU share the one array. It keeps whatever the previous call left in it; the
+ *    kernels clear what has to start at zero themselves. Two calls whose kernels overlap on the
+ *    same GPU (different streams) race on it: serialise them.
+ * Results are the same as nb_attn_bwd's up to the order of the fp32 dQ additions. */
+#define NB_ATTN_BUILTIN_SCRATCH_ROWS 65536
+int nb_attn_bwd_builtin_scratch(const nb_attn_bwd_args* args, void* stream);
 
 /* Human-readable text for a return code. */
 const char* nb_attn_strerror(int code);

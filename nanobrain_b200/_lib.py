@@ -20,7 +20,9 @@ EXPORTED_SYMBOLS = (
     "nb_attn_strerror",
     "nb_attn_abi_version",
     "nb_attn_selftest_mma",
+    "nb_attn_bwd_builtin_scratch",
 )
+BUILTIN_SCRATCH_ROWS = 65536
 
 
 class Tensor(C.Structure):
@@ -103,6 +105,8 @@ def load() -> C.CDLL:
     lib.nb_attn_fwd.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
     lib.nb_attn_bwd.restype = C.c_int
     lib.nb_attn_bwd.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
+    lib.nb_attn_bwd_builtin_scratch.restype = C.c_int
+    lib.nb_attn_bwd_builtin_scratch.argtypes = [C.POINTER(BwdArgs), C.c_void_p]
     lib.nb_attn_selftest_mma.restype = C.c_int
     lib.nb_attn_selftest_mma.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     got = lib.nb_attn_abi_version()

@@ -129,6 +129,96 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+// Scratch for nb_attn_bwd_builtin_scratch: one fixed array in the library image per GPU. The name
+// below is only a host-side handle; kernels get the device address looked up per device.
+constexpr size_t kBuiltinScratchBytes = size_t(NB_ATTN_BUILTIN_SCRATCH_ROWS) * (nb::kHeadDim * sizeof(float) + sizeof(float));
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+void* g_builtin_scratch_addr[kMaxDevices];  // device address of the array, per device, once looked up
+
+// Once per device, with that device current: resolve the array's device address.
+int builtin_scratch_address(void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return NB_ATTN_ERR_LAUNCH;
+  if (dev < 0 || dev >= kMaxDevices) return NB_ATTN_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (g_builtin_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_builtin_scratch) != cudaSuccess || ptr == nullptr) return NB_ATTN_ERR_LAUNCH;
+    g_builtin_scratch_addr[dev] = ptr;
+  }
+  *out = g_builtin_scratch_addr[dev];
+  return NB_ATTN_OK;
+}
+
+int launch_bwd(const nb_attn_bwd_args* a, void* workspace, size_t workspace_bytes, void* stream) {
+  if (a == nullptr) return NB_ATTN_ERR_NULL;
+  int rc = check_shape(a->shape);
+  if (rc) return rc;
+  const nb_attn_shape& s = a->shape;
+  const bool dense = s.cu_seqlens_q == nullptr;
+  const nb_attn_tensor* ts[] = {&a->q, &a->k, &a->v, &a->o, &a->d_o, &a->dq, &a->dk, &a->dv};
+  for (const nb_attn_tensor* t : ts)
+    if ((rc = check_tensor(*t, dense))) return rc;
+  if (a->lse == nullptr) return NB_ATTN_ERR_NULL;
+  const size_t need = nb_attn_bwd_workspace_bytes(s.total_q, s.heads, s.head_dim);
+  if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+    return NB_ATTN_ERR_WORKSPACE;
+  if ((rc = ensure_device_ready())) return rc;
+
+  CUtensorMap tq, tk, tv, tg, tdq;
+  if ((rc = make_tmap(&tq, a->q, s, true)) || (rc = make_tmap(&tk, a->k, s, false)) ||
+      (rc = make_tmap(&tv, a->v, s, false)) || (rc = make_tmap(&tg, a->d_o, s, true)) ||
+      (rc = make_dq_accum_tmap(&tdq, static_cast<float*>(workspace), s.total_q, s.heads)))
+    return rc;
+
+  nb::BwdParams p;
+  p.o = static_cast<const __nv_bfloat16*>(a->o.ptr);
+  p.d_o = static_cast<const __nv_bfloat16*>(a->d_o.ptr);
+  p.o_sb = dense ? a->o.stride_batch : 0;
+  p.o_st = a->o.stride_token;
+  p.o_sh = a->o.stride_head;
+  p.do_sb = dense ? a->d_o.stride_batch : 0;
+  p.do_st = a->d_o.stride_token;
+  p.do_sh = a->d_o.stride_head;
+  p.dq = static_cast<__nv_bfloat16*>(a->dq.ptr);
+  p.dk = static_cast<__nv_bfloat16*>(a->dk.ptr);
+  p.dv = static_cast<__nv_bfloat16*>(a->dv.ptr);
+  p.dq_sb = dense ? a->dq.stride_batch : 0;
+  p.dq_st = a->dq.stride_token;
+  p.dq_sh = a->dq.stride_head;
+  p.dk_sb = dense ? a->dk.stride_batch : 0;
+  p.dk_st = a->dk.stride_token;
+  p.dk_sh = a->dk.stride_head;
+  p.dv_sb = dense ? a->dv.stride_batch : 0;
+  p.dv_st = a->dv.stride_token;
+  p.dv_sh = a->dv.stride_head;
+  p.lse = a->lse;
+  p.dq_accum = static_cast<float*>(workspace);
+  p.delta = p.dq_accum + size_t(s.total_q) * s.heads * nb::kHeadDim;
+  p.cu_q = s.cu_seqlens_q;
+  p.cu_k = s.cu_seqlens_k;
+  p.batch = s.batch;
+  p.heads = s.heads;
+  p.lq = s.max_seqlen_q;
+  p.lk = s.max_seqlen_k;
+  p.total_q = s.total_q;
+  p.scale = s.scale;
+  p.scale_log2 = s.scale * kLog2e;
+  p.status = a->status;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t rows = s.total_q * s.heads;
+  const int64_t want_blocks = (rows * 8 + 255) / 256;
+  const int aux_blocks = int(want_blocks < 148 * 16 ? want_blocks : 148 * 16);
+  nb::attn_bwd_prologue_kernel<<<aux_blocks, 256, 0, st>>>(p);
+  if (a->event_main_begin) cudaEventRecord(static_cast<cudaEvent_t>(a->event_main_begin), st);
+  const dim3 grid(ceil_div(s.max_seqlen_k, nb::kTile), s.heads, s.batch);
+  nb::attn_bwd_kernel<<<grid, nb::kBwdThreads, nb::kBwdSmemBytes, st>>>(tq, tk, tv, tg, tdq, p);
+  if (a->event_main_end) cudaEventRecord(static_cast<cudaEvent_t>(a->event_main_end), st);
+  nb::attn_bwd_epilogue_kernel<<<aux_blocks, 256, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? NB_ATTN_OK : NB_ATTN_ERR_LAUNCH;
+}
+
 }  // namespace
 
 extern "C" {
@@ -146,6 +236,8 @@ const char* nb_attn_strerror(int code) {
     case NB_ATTN_ERR_TENSOR_MAP: return "could not encode a TMA tensor map";
     case NB_ATTN_ERR_LAUNCH: return "a CUDA runtime call failed";
     case NB_ATTN_ERR_DEVICE: return "the current device is not an sm_100 GPU";
+    case NB_ATTN_ERR_TOO_LARGE:
+      return "total_q * heads exceeds NB_ATTN_BUILTIN_SCRATCH_ROWS; use nb_attn_bwd with a caller workspace";
     default: return "unknown error code";
   }
 }
@@ -196,71 +288,17 @@ int nb_attn_fwd(const nb_attn_fwd_args* a, void* stream) {
 
 int nb_attn_bwd(const nb_attn_bwd_args* a, void* stream) {
   if (a == nullptr) return NB_ATTN_ERR_NULL;
+  return launch_bwd(a, a->workspace, a->workspace_bytes, stream);
+}
+
+int nb_attn_bwd_builtin_scratch(const nb_attn_bwd_args* a, void* stream) {
+  if (a == nullptr) return NB_ATTN_ERR_NULL;
   int rc = check_shape(a->shape);
   if (rc) return rc;
-  const nb_attn_shape& s = a->shape;
-  const bool dense = s.cu_seqlens_q == nullptr;
-  const nb_attn_tensor* ts[] = {&a->q, &a->k, &a->v, &a->o, &a->d_o, &a->dq, &a->dk, &a->dv};
-  for (const nb_attn_tensor* t : ts)
-    if ((rc = check_tensor(*t, dense))) return rc;
-  if (a->lse == nullptr) return NB_ATTN_ERR_NULL;
-  const size_t need = nb_attn_bwd_workspace_bytes(s.total_q, s.heads, s.head_dim);
-  if (a->workspace == nullptr || a->workspace_bytes < need || (reinterpret_cast<uintptr_t>(a->workspace) & 255u) != 0)
-    return NB_ATTN_ERR_WORKSPACE;
-  if ((rc = ensure_device_ready())) return rc;
-
-  CUtensorMap tq, tk, tv, tg, tdq;
-  if ((rc = make_tmap(&tq, a->q, s, true)) || (rc = make_tmap(&tk, a->k, s, false)) ||
-      (rc = make_tmap(&tv, a->v, s, false)) || (rc = make_tmap(&tg, a->d_o, s, true)) ||
-      (rc = make_dq_accum_tmap(&tdq, static_cast<float*>(a->workspace), s.total_q, s.heads)))
-    return rc;
-
-  nb::BwdParams p;
-  p.o = static_cast<const __nv_bfloat16*>(a->o.ptr);
-  p.d_o = static_cast<const __nv_bfloat16*>(a->d_o.ptr);
-  p.o_sb = dense ? a->o.stride_batch : 0;
-  p.o_st = a->o.stride_token;
-  p.o_sh = a->o.stride_head;
-  p.do_sb = dense ? a->d_o.stride_batch : 0;
-  p.do_st = a->d_o.stride_token;
-  p.do_sh = a->d_o.stride_head;
-  p.dq = static_cast<__nv_bfloat16*>(a->dq.ptr);
-  p.dk = static_cast<__nv_bfloat16*>(a->dk.ptr);
-  p.dv = static_cast<__nv_bfloat16*>(a->dv.ptr);
-  p.dq_sb = dense ? a->dq.stride_batch : 0;
-  p.dq_st = a->dq.stride_token;
-  p.dq_sh = a->dq.stride_head;
-  p.dk_sb = dense ? a->dk.stride_batch : 0;
-  p.dk_st = a->dk.stride_token;
-  p.dk_sh = a->dk.stride_head;
-  p.dv_sb = dense ? a->dv.stride_batch : 0;
-  p.dv_st = a->dv.stride_token;
-  p.dv_sh = a->dv.stride_head;
-  p.lse = a->lse;
-  p.dq_accum = static_cast<float*>(a->workspace);
-  p.delta = p.dq_accum + size_t(s.total_q) * s.heads * nb::kHeadDim;
-  p.cu_q = s.cu_seqlens_q;
-  p.cu_k = s.cu_seqlens_k;
-  p.batch = s.batch;
-  p.heads = s.heads;
-  p.lq = s.max_seqlen_q;
-  p.lk = s.max_seqlen_k;
-  p.total_q = s.total_q;
-  p.scale = s.scale;
-  p.scale_log2 = s.scale * kLog2e;
-  p.status = a->status;
-
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t rows = s.total_q * s.heads;
-  const int64_t want_blocks = (rows * 8 + 255) / 256;
-  const int aux_blocks = int(want_blocks < 148 * 16 ? want_blocks : 148 * 16);
-  nb::attn_bwd_prologue_kernel<<<aux_blocks, 256, 0, st>>>(p);
-  if (a->event_main_begin) cudaEventRecord(static_cast<cudaEvent_t>(a->event_main_begin), st);
-  const dim3 grid(ceil_div(s.max_seqlen_k, nb::kTile), s.heads, s.batch);
-  nb::attn_bwd_kernel<<<grid, nb::kBwdThreads, nb::kBwdSmemBytes, st>>>(tq, tk, tv, tg, tdq, p);
-  if (a->event_main_end) cudaEventRecord(static_cast<cudaEvent_t>(a->event_main_end), st);
-  nb::attn_bwd_epilogue_kernel<<<aux_blocks, 256, 0, st>>>(p);
-  return cudaGetLastError() == cudaSuccess ? NB_ATTN_OK : NB_ATTN_ERR_LAUNCH;
+  if (a->shape.total_q * int64_t(a->shape.heads) > int64_t(NB_ATTN_BUILTIN_SCRATCH_ROWS)) return NB_ATTN_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  if ((rc = builtin_scratch_address(&scratch))) return rc;
+  return launch_bwd(a, scratch, kBuiltinScratchBytes, stream);
 }
 
 int nb_attn_selftest_mma(int mode, const void* a, const void* b, float* d, int32_t* status, void* stream) {

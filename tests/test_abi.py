@@ -36,8 +36,8 @@ def test_library_exports_every_declared_symbol(lib):
 def test_abi_version_and_strerror(lib):
     assert lib.nb_attn_abi_version() == _lib.ABI_VERSION
     assert lib.nb_attn_strerror(0) == b"ok"
-    texts = {lib.nb_attn_strerror(c) for c in range(1, 9)}
-    assert len(texts) == 8 and b"unknown error code" not in texts
+    texts = {lib.nb_attn_strerror(c) for c in range(1, 10)}
+    assert len(texts) == 9 and b"unknown error code" not in texts
     assert lib.nb_attn_strerror(999) == b"unknown error code"
 
 
