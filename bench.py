@@ -133,6 +133,31 @@ class ClockSampler:
         }
 
 
+def gather_over_ranks(stats, world: int):
+    """All-gather one row of per-rank numbers (a 1-D tensor) -> [world, n] tensor on the CPU.
+    Works for NCCL (CUDA tensors) and gloo (CPU tensors); world == 1 needs no process group."""
+    import torch
+    import torch.distributed as dist
+
+    if world == 1:
+        return stats[None].cpu()
+    gathered = [torch.zeros_like(stats) for _ in range(world)]
+    dist.all_gather(gathered, stats)
+    return torch.stack(gathered).cpu()
+
+
+def aggregate(allstats, steps: int):
+    """Whole-job numbers from per-rank rows [elapsed_ms, e2e_ms_per_step, flops_per_step, tokens]:
+    time is the MAX over ranks, work is the SUM over ranks."""
+    max_ms, max_e2e_ms = float(allstats[:, 0].max()), float(allstats[:, 1].max())
+    flops_all, tokens_all = float(allstats[:, 2].sum()), int(allstats[:, 3].sum())
+    return {
+        "max_ms": max_ms, "max_e2e_ms": max_e2e_ms, "flops_all": flops_all, "tokens_all": tokens_all,
+        "value_tflops": flops_all * steps / (max_ms * 1e-3) / 1e12,
+        "e2e_tflops": flops_all / (max_e2e_ms * 1e-3) / 1e12,
+    }
+
+
 def rank_lengths(args, rank: int, world: int):
     from nanobrain_b200 import workloads as W
 
@@ -307,19 +332,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # Max over ranks of the device times; sums of the work.
     stats = torch.tensor([elapsed_ms, e2e_ms, float(flops_step), float(total)], dtype=torch.float64, device=dev)
-    if world > 1:
-        gathered = [torch.zeros_like(stats) for _ in range(world)]
-        dist.all_gather(gathered, stats)
-        allstats = torch.stack(gathered).cpu()
-    else:
-        allstats = stats[None].cpu()
-    max_ms, max_e2e_ms = float(allstats[:, 0].max()), float(allstats[:, 1].max())
-    flops_all, tokens_all = float(allstats[:, 2].sum()), int(allstats[:, 3].sum())
+    agg = aggregate(gather_over_ranks(stats, world), args.steps)
+    max_ms, max_e2e_ms = agg["max_ms"], agg["max_e2e_ms"]
+    flops_all, tokens_all = agg["flops_all"], agg["tokens_all"]
 
     if rank == 0:
         peaks, peak_kind = load_peaks()
-        value = flops_all * args.steps / (max_ms * 1e-3) / 1e12
-        e2e_value = flops_all / (max_e2e_ms * 1e-3) / 1e12
+        value, e2e_value = agg["value_tflops"], agg["e2e_tflops"]
         bytes_tensor = total * heads * W.HEAD_DIM * 2
         bwd_flops = W.attention_flops(lengths, lengths, heads, fwd=False, bwd=True)
         achieved = bwd_flops / (bwd_main_ms * 1e-3) / 1e12
