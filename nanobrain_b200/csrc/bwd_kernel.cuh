@@ -480,7 +480,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tmem_ld32(tm_dq + lane_off + 32 * w, rq);
         tmem_wait_ld();
         reduce_dq((n_q - 1 + kt) % n_q, rq);
-        if (lane == 0) bulk_wait_group0();  // all reductions of this warp have landed
+        if (lane == 0) bulk_wait_group_read0();  // the staging rows must outlive the TMA engine's reads
       }
 
       // ---- epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK (scaled) ----
