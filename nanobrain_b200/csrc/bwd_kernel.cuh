@@ -14,13 +14,15 @@
 //                                dQ   = dS K                        (same dS bytes read MN-major)
 //                              dQ tiles are added into the fp32 accumulator with TMA add-reductions
 //                              because every K/V tile of a sequence contributes to every dQ row.
-//                              Warp roles (512 threads): warps 0-7 are two compute warpgroups that
+//                              Warp roles (640 threads): warps 0-7 are two compute warpgroups that
 //                              split the 128 query columns of a tile (64 each); warps 8-11 are
 //                              four MMA issuers (S^T/dP^T, dV, dK, dQ: one elected thread each --
 //                              a single thread can issue a tcgen05.mma only every ~55 cycles, so
 //                              the 32 MMAs of a tile need several issuers to keep the tensor pipe
-//                              fed); warp 12 drives TMA and stages LSE/delta rows (warps 13-15 only complete its
-//                              warpgroup for the register re-partitioning).
+//                              fed); warps 12-15 drain the dQ tiles (one tensor-memory lane
+//                              quadrant each) into the accumulator; warp 16 drives TMA and stages
+//                              LSE/delta rows (warps 17-19 only complete its warpgroup for the
+//                              register re-partitioning).
 //   attn_bwd_epilogue_kernel : dQ = bf16(scale * accumulator). HBM-bound.
 #pragma once
 
@@ -119,23 +121,25 @@ __global__ void __launch_bounds__(256) attn_bwd_epilogue_kernel(const BwdParams 
 // ----------------------------------------------------------------------------------------
 // Main backward kernel
 // ----------------------------------------------------------------------------------------
-constexpr int kBwdThreads = 512;
+constexpr int kBwdThreads = 640;
 constexpr int kBwdStages = 3;  // Q/dO ring
 // K, V, 3x(Q, dO), dS (two 64-column halves), fp32 dQ staging (two 32-column halves) + LSE/delta
 // stages + alignment slack
 constexpr int kBwdSmemBytes = (2 + 2 * kBwdStages + 4) * kTileBytes + kBwdStages * 2 * kTile * 4 + 1024;
 constexpr int kBwdTmemCols = 512;  // S^T 0, dP^T 128, P^T 256, dV 320, dK 384, dQ 448
-// Register re-partitioning. The CTA launches with 512 threads x 128 registers (the whole register
-// file of the SM); setmaxnreg only moves registers inside that allocation, so the budget must
-// balance exactly or the growing warps would wait for ever:
-//   2 compute warpgroups x 128 threads x 208 + issuer warpgroup x 128 x 56 + TMA warpgroup x 128 x 40
-//   = 53248 + 7168 + 5120 = 65536 = 512 x 128.
-// Every warp of an aligned warpgroup executes the same setmaxnreg instruction (warps 13-15 exist
-// only to complete the TMA warp's warpgroup).
-constexpr int kBwdComputeRegs = 208;
+// Register re-partitioning. The CTA launches with 640 threads x 96 registers (the most the
+// register file allows); setmaxnreg only moves registers inside that allocation, so the budget
+// must balance exactly or the growing warps would wait for ever:
+//   2 compute warpgroups x 128 x 168 + issuers 128 x 56 + dQ drainers 128 x 56 + loader group 128 x 32
+//   = 43008 + 7168 + 7168 + 4096 = 61440 = 640 x 96.
+// Every warp of an aligned warpgroup executes the same setmaxnreg instruction.
+constexpr int kBwdLaunchRegs = 96;
+constexpr int kBwdComputeRegs = 168;
 constexpr int kBwdIssuerRegs = 56;
-constexpr int kBwdLoaderRegs = 40;
-static_assert(256 * kBwdComputeRegs + 128 * kBwdIssuerRegs + 128 * kBwdLoaderRegs == 512 * 128, "register budget");
+constexpr int kBwdDrainRegs = 56;
+constexpr int kBwdLoaderRegs = 32;
+static_assert(256 * kBwdComputeRegs + 128 * (kBwdIssuerRegs + kBwdDrainRegs + kBwdLoaderRegs) ==
+                  kBwdThreads * kBwdLaunchRegs, "register budget");
 
 enum BwdBar : int {
   kBarKvFull = 0,
@@ -150,7 +154,7 @@ enum BwdBar : int {
   kBarDsFull,   // 8 arrivals
   kBarDsFree,   // 2 arrivals: dK and dQ issuers
   kBarDqFull,
-  kBarDqFree,   // 8
+  kBarDqFree,   // 4 (dQ drain warps)
   kBarDkDone,
   kBwdNumBars
 };
@@ -202,7 +206,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     for (int i = 0; i < kBwdNumBars; ++i) {
       uint32_t count = 1;
       if (i >= kBarQdoEmpty && i < kBarQdoEmpty + kBwdStages) count = 3;
-      if (i == kBarSFree || i == kBarDpFree || i == kBarPFull || i == kBarDqFree) count = 8;
+      if (i == kBarSFree || i == kBarDpFree || i == kBarPFull) count = 8;
+      if (i == kBarDqFree) count = 4;
       if (i == kBarDsFull) count = 8;
       if (i == kBarDsFree) count = 2;
       mbar_init(bar(i), count);
@@ -226,10 +231,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int64_t stat_base = p.cu_q != nullptr ? int64_t(h) * p.total_q + q_begin : (int64_t(b) * p.heads + h) * p.lq;
 
   if (n_q > 0) {
-    if (warp >= 12) {
-      // ---------------- TMA producer + LSE/delta staging (warp 12; 13-15 idle) ----------------
+    if (warp >= 16) {
+      // ---------------- TMA producer + LSE/delta staging (warp 16; 17-19 idle) ----------------
       setmaxnreg_dec<kBwdLoaderRegs>();
-      if (warp == 12) {
+      if (warp == 16) {
       if (lane == 0) {
         tma_prefetch_desc(&tmap_q);
         tma_prefetch_desc(&tmap_k);
@@ -266,6 +271,48 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
       }
       }
+    } else if (warp >= 12) {
+      // ---------------- dQ drain warps: tensor memory -> staged fp32 rows -> TMA add-reduction ----------------
+      // Warp 12+q owns tensor-memory lane quadrant q. It stages its 32 rows (two 32-column halves,
+      // 128-byte swizzled rows) in shared memory and one lane issues the TMA add-reductions, so
+      // only warp-level synchronisation is needed and L2 receives whole 128-byte lines. Rows past
+      // the end of the sequence hold exact zeros (their P^T column is 0), so adding them is harmless.
+      setmaxnreg_dec<kBwdDrainRegs>();
+      const int quad = warp & 3;
+      const uint32_t lane_off = uint32_t(quad * 32) << 16;
+      const int64_t acc_batch_row = int64_t(p.cu_q != nullptr ? 0 : b) * p.lq + q_begin;
+      uint8_t* stage = sDQ_ptr + quad * 4096;
+      for (int j = 0; j < n_q; ++j) {
+        const int tile = (j + kt) % n_q;
+        mbar_wait(bar(kBarDqFull), j & 1, &abort_flag, p.status);
+        tc_fence_after();
+        if (lane == 0) bulk_wait_group_read0();  // the previous reductions have read the staging rows
+        __syncwarp();
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r[32];
+          tmem_ld32(tm_dq + lane_off + 32 * half, r);
+          tmem_wait_ld();
+          if (half == 1) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(kBarDqFree));  // the dQ tile is out of tensor memory
+          }
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(stage + half * kTileBytes + swz128(lane, c)) =
+                make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int row = int(acc_batch_row) + tile * kTile + quad * 32;
+          tma_reduce_add_3d(&tmap_dq, smem_u32(stage), 0, row, h);
+          tma_reduce_add_3d(&tmap_dq, smem_u32(stage + kTileBytes), 32, row, h);
+          bulk_commit_group();
+        }
+      }
+      if (lane == 0) bulk_wait_group_read0();  // the staging rows must outlive the TMA engine's reads
     } else if (warp >= 8) {
       setmaxnreg_dec<kBwdIssuerRegs>();
       if (warp == 8) {
@@ -352,27 +399,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const bool row_valid = (k_row0 + krow_in_tile) < lk;
       const bool partial = (k_row0 + kTile) > lk;
       const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
-      const int64_t acc_batch_row = int64_t(p.cu_q != nullptr ? 0 : b) * p.lq + q_begin;
-
-      // dQ tile -> fp32 accumulator. Each warp stages its 32 rows x 32 columns (fp32, 128-byte
-      // swizzled rows) in shared memory and one lane issues a TMA add-reduction for that 4 KB box,
-      // so only warp-level synchronisation is needed and L2 receives whole 128-byte lines. Rows past
-      // the end of the sequence hold exact zeros (their P^T column is 0), so adding them is harmless.
-      uint8_t* dq_stage = sDQ_ptr + w * kTileBytes + (warp & 3) * 4096;
-      auto reduce_dq = [&](int tile, const uint32_t (&r)[32]) {
-        if (lane == 0) bulk_wait_group_read0();  // the previous reduction has read the staging rows
-        __syncwarp();
-#pragma unroll
-        for (int c = 0; c < 8; ++c)
-          *reinterpret_cast<uint4*>(dq_stage + swz128(lane, c)) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_reduce_add_3d(&tmap_dq, smem_u32(dq_stage), 32 * w, int(acc_batch_row) + tile * kTile + (warp & 3) * 32, h);
-          bulk_commit_group();
-        }
-      };
-
       for (int j = 0; j < n_q; ++j) {
         const int qs = j % kBwdStages;
         const float4* lse4 = reinterpret_cast<const float4*>(sLse + qs * kTile + 64 * w);   // -lse (log2)
@@ -426,16 +452,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           }
         }
 
-        // ---- middle: pull dQ of the previous tile and dP^T of this tile out of tensor memory ----
-        uint32_t rq[32], ra[32], rb[32];
-        if (j > 0) {
-          mbar_wait2(bar(kBarDqFull), (j - 1) & 1, bar(kBarDpFull), j & 1, &abort_flag, p.status);
-          tc_fence_after();
-          tmem_ld32(tm_dq + lane_off + 32 * w, rq);
-        } else {
-          mbar_wait(bar(kBarDpFull), j & 1, &abort_flag, p.status);
-          tc_fence_after();
-        }
+        // ---- middle: pull dP^T of this tile out of tensor memory ----
+        uint32_t ra[32], rb[32];
+        mbar_wait(bar(kBarDpFull), j & 1, &abort_flag, p.status);
+        tc_fence_after();
         tmem_ld32(tm_dp + lane_off + 64 * w, ra);
         tmem_ld32(tm_dp + lane_off + 64 * w + 32, rb);
         tmem_wait_ld();
@@ -444,10 +464,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(bar(kBarPFull));
-          if (j > 0) mbar_arrive(bar(kBarDqFree));
           mbar_arrive(bar(kBarDpFree));
         }
-        if (j > 0) reduce_dq((j - 1 + kt) % n_q, rq);
 
         // ---- phase B: dS^T = P^T o (dP^T - delta) -> shared memory ----
         if (j > 0) mbar_wait(bar(kBarDsFree), (j - 1) & 1, &abort_flag, p.status);
@@ -472,17 +490,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kBarDsFull));
       }
-      {
-        // dQ of the last query tile.
-        uint32_t rq[32];
-        mbar_wait(bar(kBarDqFull), (n_q - 1) & 1, &abort_flag, p.status);
-        tc_fence_after();
-        tmem_ld32(tm_dq + lane_off + 32 * w, rq);
-        tmem_wait_ld();
-        reduce_dq((n_q - 1 + kt) % n_q, rq);
-        if (lane == 0) bulk_wait_group_read0();  // the staging rows must outlive the TMA engine's reads
-      }
-
       // ---- epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK (scaled) ----
       if (w == 0) mbar_wait(bar(kBarPtFree), (n_q - 1) & 1, &abort_flag, p.status);
       else mbar_wait(bar(kBarDkDone), 0, &abort_flag, p.status);
