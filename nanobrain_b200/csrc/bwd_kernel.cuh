@@ -405,6 +405,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         const float4* dl4 = reinterpret_cast<const float4*>(sDelta + qs * kTile + 64 * w);  // -delta
         uint64_t pf[32];  // P^T values of this thread as packed fp32 pairs
 
+        bool pt_ok, dp_ok;
         // ---- phase A: P^T = exp2(S^T * scale_log2 - lse) ----
         mbar_wait2(bar(kBarQdoFull + qs), (j / kBwdStages) & 1, bar(kBarSFull), j & 1, &abort_flag, p.status);
         tc_fence_after();
@@ -416,6 +417,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(kBarSFree));
+          // Poll the barriers needed after the exponentials now; the polls' latency overlaps them.
+          pt_ok = j > 0 ? mbar_try_wait(bar(kBarPtFree), (j - 1) & 1) : true;
+          dp_ok = mbar_try_wait(bar(kBarDpFull), j & 1);
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const uint32_t* src = i < 8 ? &ra[4 * i] : &rb[4 * (i - 8)];
@@ -435,7 +439,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           for (int i = 0; i < 32; ++i) pf[i] = 0ull;
         }
         if (j > 0) {
-          mbar_wait(bar(kBarPtFree), (j - 1) & 1, &abort_flag, p.status);
+          if (!pt_ok) mbar_wait(bar(kBarPtFree), (j - 1) & 1, &abort_flag, p.status);
           tc_fence_after();
         }
         {
@@ -454,8 +458,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
 
         // ---- middle: pull dP^T of this tile out of tensor memory ----
         uint32_t ra[32], rb[32];
-        mbar_wait(bar(kBarDpFull), j & 1, &abort_flag, p.status);
+        if (!dp_ok) mbar_wait(bar(kBarDpFull), j & 1, &abort_flag, p.status);
         tc_fence_after();
+        const bool ds_ok = j > 0 ? mbar_try_wait(bar(kBarDsFree), (j - 1) & 1) : true;
         tmem_ld32(tm_dp + lane_off + 64 * w, ra);
         tmem_ld32(tm_dp + lane_off + 64 * w + 32, rb);
         tmem_wait_ld();
@@ -468,7 +473,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         }
 
         // ---- phase B: dS^T = P^T o (dP^T - delta) -> shared memory ----
-        if (j > 0) mbar_wait(bar(kBarDsFree), (j - 1) & 1, &abort_flag, p.status);
+        if (!ds_ok) mbar_wait(bar(kBarDsFree), (j - 1) & 1, &abort_flag, p.status);
         uint8_t* half = sDS_ptr + w * kTileBytes;
 #pragma unroll
         for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = query columns [8c, 8c+8) of this half
