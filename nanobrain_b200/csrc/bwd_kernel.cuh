@@ -430,7 +430,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
             unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(src[2]), __uint_as_float(src[3])), scale2,
                                    pack_f32x2(l.z, l.w)), x2, x3);
             pf[2 * i] = pack_f32x2(fast_exp2(x0), fast_exp2(x1));
-            pf[2 * i + 1] = pack_f32x2(fast_exp2(x2), fast_exp2(x3));
+            // Every other second pair goes to the FMA pipe: the exponentials are this phase's
+            // bottleneck (both warps of an SM sub-partition run it together on one MUFU unit).
+            if (i & 1) pf[2 * i + 1] = exp2_poly_f32x2(pack_f32x2(x2, x3));
+            else pf[2 * i + 1] = pack_f32x2(fast_exp2(x2), fast_exp2(x3));
           }
         }
         if (partial && !row_valid) {
