@@ -205,6 +205,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     abort_flag = 0;
     for (int i = 0; i < kBwdNumBars; ++i) {
       uint32_t count = 1;
+      if (i >= kBarQdoFull && i < kBarQdoFull + kBwdStages) count = 2;  // TMA issue + LSE/delta staged
       if (i >= kBarQdoEmpty && i < kBarQdoEmpty + kBwdStages) count = 3;
       if (i == kBarSFree || i == kBarDpFree || i == kBarPFull) count = 8;
       if (i == kBarDqFree) count = 4;
@@ -250,6 +251,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (j >= kBwdStages && lane == 0)
           mbar_wait(bar(kBarQdoEmpty + qs), ((j / kBwdStages) - 1) & 1, &abort_flag, p.status);
         __syncwarp();
+        // TMA first, so that its latency overlaps the LSE/delta loads below.
+        if (lane == 0) {
+          mbar_arrive_expect_tx(bar(kBarQdoFull + qs), 2 * kTileBytes);
+          tma_load_4d(sQ(qs), &tmap_q, bar(kBarQdoFull + qs), 0, q_begin + jt * kTile, h, bcoord);
+          tma_load_4d(sDO(qs), &tmap_do, bar(kBarQdoFull + qs), 0, q_begin + jt * kTile, h, bcoord);
+        }
         // Staged negated: -lse in the log2 domain and -delta. Rows past the end of the sequence get
         // -lse = -inf, which makes their P^T column exactly 0.
 #pragma unroll
@@ -264,11 +271,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           sDelta[qs * kTile + r4 * 32 + lane] = dl;
         }
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive_expect_tx(bar(kBarQdoFull + qs), 2 * kTileBytes);
-          tma_load_4d(sQ(qs), &tmap_q, bar(kBarQdoFull + qs), 0, q_begin + jt * kTile, h, bcoord);
-          tma_load_4d(sDO(qs), &tmap_do, bar(kBarQdoFull + qs), 0, q_begin + jt * kTile, h, bcoord);
-        }
+        if (lane == 0) mbar_arrive(bar(kBarQdoFull + qs));
       }
       }
     } else if (warp >= 12) {
@@ -499,30 +502,39 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (lane == 0) mbar_arrive(bar(kBarDsFull));
       }
       // ---- epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK (scaled) ----
-      if (w == 0) mbar_wait(bar(kBarPtFree), (n_q - 1) & 1, &abort_flag, p.status);
-      else mbar_wait(bar(kBarDkDone), 0, &abort_flag, p.status);
+      // Both accumulators complete, and with them every MMA that reads the Q/dO stages reused below.
+      mbar_wait2(bar(kBarPtFree), (n_q - 1) & 1, bar(kBarDkDone), 0, &abort_flag, p.status);
       tc_fence_after();
-      const int krow = k_row0 + krow_in_tile;
-      __nv_bfloat16* out_ptr =
-          w == 0 ? p.dv + int64_t(bcoord) * p.dv_sb + int64_t(k_begin + krow) * p.dv_st + int64_t(h) * p.dv_sh
-                 : p.dk + int64_t(bcoord) * p.dk_sb + int64_t(k_begin + krow) * p.dk_st + int64_t(h) * p.dk_sh;
+      // Each warp turns its 32 accumulator rows into bf16 in a 4 KB scratch area (a Q/dO stage,
+      // dead by now) and writes them out with eight lanes per 128-byte row, so the stores are whole
+      // lines. Only warp-level synchronisation is needed: a warp reads back what it wrote.
+      uint8_t* scratch = smem_al + (2 + w) * kTileBytes + (warp & 3) * 4096;
       const float out_scale = w == 0 ? 1.f : p.scale;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t r[32];
         tmem_ld32((w == 0 ? tm_dv : tm_dk) + lane_off + c * 32, r);
         tmem_wait_ld();
-        if (krow < lk) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(r[8 * i + 0]) * out_scale, __uint_as_float(r[8 * i + 1]) * out_scale);
-            v.y = pack_bf16(__uint_as_float(r[8 * i + 2]) * out_scale, __uint_as_float(r[8 * i + 3]) * out_scale);
-            v.z = pack_bf16(__uint_as_float(r[8 * i + 4]) * out_scale, __uint_as_float(r[8 * i + 5]) * out_scale);
-            v.w = pack_bf16(__uint_as_float(r[8 * i + 6]) * out_scale, __uint_as_float(r[8 * i + 7]) * out_scale);
-            reinterpret_cast<uint4*>(out_ptr)[c * 4 + i] = v;
-          }
+        for (int i = 0; i < 4; ++i) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(r[8 * i + 0]) * out_scale, __uint_as_float(r[8 * i + 1]) * out_scale);
+          v.y = pack_bf16(__uint_as_float(r[8 * i + 2]) * out_scale, __uint_as_float(r[8 * i + 3]) * out_scale);
+          v.z = pack_bf16(__uint_as_float(r[8 * i + 4]) * out_scale, __uint_as_float(r[8 * i + 5]) * out_scale);
+          v.w = pack_bf16(__uint_as_float(r[8 * i + 6]) * out_scale, __uint_as_float(r[8 * i + 7]) * out_scale);
+          *reinterpret_cast<uint4*>(scratch + swz128(lane, c * 4 + i)) = v;
         }
+      }
+      __syncwarp();
+      __nv_bfloat16* out_base = w == 0 ? p.dv + int64_t(bcoord) * p.dv_sb + int64_t(h) * p.dv_sh
+                                       : p.dk + int64_t(bcoord) * p.dk_sb + int64_t(h) * p.dk_sh;
+      const int64_t out_st = w == 0 ? p.dv_st : p.dk_st;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int rloc = it * 4 + (lane >> 3);
+        const int krow = k_row0 + (warp & 3) * 32 + rloc;
+        const uint4 v = *reinterpret_cast<const uint4*>(scratch + swz128(rloc, lane & 7));
+        if (krow < lk) *reinterpret_cast<uint4*>(out_base + int64_t(k_begin + krow) * out_st + (lane & 7) * 8) = v;
       }
     }
   } else if (warp < 8) {

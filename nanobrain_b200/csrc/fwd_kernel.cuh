@@ -270,23 +270,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       tc_fence_after();
       const int row = q_row0 + tid;
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* optr = p.o + int64_t(bcoord) * p.o_sb + int64_t(q_begin + row) * p.o_st + int64_t(h) * p.o_sh;
+      // Each warp turns its 32 rows into bf16 in a 4 KB scratch area (the Q tile, dead once the
+      // last S MMA has run -- which the completed P V MMA implies) and writes them out with eight
+      // lanes per 128-byte row, so the stores are whole lines; a warp only reads what it wrote.
+      uint8_t* scratch = smem_raw + (smem_base - smem_u32(smem_raw)) + warp * 4096;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t o[32];
         tmem_ld32(o_addr + c * 32, o);
         tmem_wait_ld();
-        if (row < lq) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(o[8 * j + 0]) * inv_l, __uint_as_float(o[8 * j + 1]) * inv_l);
-            v.y = pack_bf16(__uint_as_float(o[8 * j + 2]) * inv_l, __uint_as_float(o[8 * j + 3]) * inv_l);
-            v.z = pack_bf16(__uint_as_float(o[8 * j + 4]) * inv_l, __uint_as_float(o[8 * j + 5]) * inv_l);
-            v.w = pack_bf16(__uint_as_float(o[8 * j + 6]) * inv_l, __uint_as_float(o[8 * j + 7]) * inv_l);
-            reinterpret_cast<uint4*>(optr)[c * 4 + j] = v;
-          }
+        for (int j = 0; j < 4; ++j) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(o[8 * j + 0]) * inv_l, __uint_as_float(o[8 * j + 1]) * inv_l);
+          v.y = pack_bf16(__uint_as_float(o[8 * j + 2]) * inv_l, __uint_as_float(o[8 * j + 3]) * inv_l);
+          v.z = pack_bf16(__uint_as_float(o[8 * j + 4]) * inv_l, __uint_as_float(o[8 * j + 5]) * inv_l);
+          v.w = pack_bf16(__uint_as_float(o[8 * j + 6]) * inv_l, __uint_as_float(o[8 * j + 7]) * inv_l);
+          *reinterpret_cast<uint4*>(scratch + swz128(lane, c * 4 + j)) = v;
         }
+      }
+      __syncwarp();
+      __nv_bfloat16* out_base = p.o + int64_t(bcoord) * p.o_sb + int64_t(h) * p.o_sh;
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int rloc = it * 4 + (lane >> 3);
+        const int orow = q_row0 + warp * 32 + rloc;
+        const uint4 v = *reinterpret_cast<const uint4*>(scratch + swz128(rloc, lane & 7));
+        if (orow < lq) *reinterpret_cast<uint4*>(out_base + int64_t(q_begin + orow) * p.o_st + (lane & 7) * 8) = v;
       }
       if (row < lq) {
         const float lse = (m_run * p.scale_log2 + log2f(l_run)) * 0.6931471805599453f;
