@@ -502,13 +502,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         if (lane == 0) mbar_arrive(bar(kBarDsFull));
       }
       // ---- epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK (scaled) ----
-      // Both accumulators complete, and with them every MMA that reads the Q/dO stages reused below.
-      mbar_wait2(bar(kBarPtFree), (n_q - 1) & 1, bar(kBarDkDone), 0, &abort_flag, p.status);
+      // Warpgroup 0 needs dV complete (the last P^T consumed), warpgroup 1 needs dK complete.
+      if (w == 0) mbar_wait(bar(kBarPtFree), (n_q - 1) & 1, &abort_flag, p.status);
+      else mbar_wait(bar(kBarDkDone), 0, &abort_flag, p.status);
       tc_fence_after();
-      // Each warp turns its 32 accumulator rows into bf16 in a 4 KB scratch area (a Q/dO stage,
-      // dead by now) and writes them out with eight lanes per 128-byte row, so the stores are whole
-      // lines. Only warp-level synchronisation is needed: a warp reads back what it wrote.
-      uint8_t* scratch = smem_al + (2 + w) * kTileBytes + (warp & 3) * 4096;
+      // Each warp turns its 32 accumulator rows into bf16 in a 4 KB scratch area and writes them out
+      // with eight lanes per 128-byte row, so the stores are whole lines. Only warp-level
+      // synchronisation is needed: a warp reads back what it wrote. The scratch is dead operand
+      // space: warpgroup 0 uses the V tile (last read by the final dP^T MMA, long complete when the
+      // final dV MMA is), warpgroup 1 the first Q stage (read only by S^T and dK MMAs, all complete).
+      uint8_t* scratch = smem_al + (1 + w) * kTileBytes + (warp & 3) * 4096;
       const float out_scale = w == 0 ? 1.f : p.scale;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
