@@ -39,6 +39,9 @@ METRIC = "attn_fwd_bwd_tflops"
 UNIT = "TFLOP/s"
 NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_bwd_kernel launch, from the ncu capture
+# summarised in profiles/attn_kernels_vitb_encoder_varlen.md (only known for that workload).
+NCU_DRAM_BYTES_BWD_MAIN = {"vitb_encoder_varlen": 365.3e6}
 
 
 def parse_args():
@@ -364,7 +367,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 "kernel": "attn_bwd_kernel", "bound": "tensor", "achieved": achieved, "peak": peak,
                 "unit": UNIT, "frac": achieved / peak, "peak_source": f"{peak_kind} bf16_tflops (burst)",
                 "ms_per_launch": bwd_main_ms, "launches_timed": n_probe,
-                "algorithmic_flops_per_launch": bwd_flops, "traffic": None,
+                "algorithmic_flops_per_launch": bwd_flops,
+                "traffic": NCU_DRAM_BYTES_BWD_MAIN.get(args.workload) if not args.global_batch else None,
+                "traffic_unit": "bytes of DRAM traffic per launch (ncu, rank-0 batch shape)",
             },
         }
         if world == 1 and not args.skip_cpu_baseline:
