@@ -207,6 +207,10 @@ def cpu_reference_tflops(lengths, heads, budget_s: float, steps: int = 1, warmup
 def run_reference(args, rank: int, world: int):
     if rank != 0:
         return
+    import torch
+
+    # torch.distributed.run exports OMP_NUM_THREADS=1; the reference arm uses every host core it may.
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     w, lengths, scaling = rank_lengths(args, 0, 1)
     tflops, info = cpu_reference_tflops(lengths, w.heads, budget_s=150.0, steps=args.steps, warmup=max(args.warmup, 1))
     line = {
@@ -373,6 +377,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             },
         }
         if world == 1 and not args.skip_cpu_baseline:
+            torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
             tf, info = cpu_reference_tflops(lengths, heads, budget_s=20.0, steps=3, warmup=1)
             line["cpu_baseline"] = {"value": tf, "unit": UNIT, "cores": info["cores"], "kind": "reference",
                                     "sample": info["sample"], "host_cpus": info["host_cpus"]}

@@ -16,7 +16,7 @@
 //   warp 4    : one elected thread issues every tcgen05.mma: S = Q K^T (both operands from shared
 //               memory) and O += P V (P from tensor memory, V from shared memory, MN-major).
 //   warp 5    : one elected thread drives TMA: the Q tile once, then K and V tiles through a
-//               two-stage ring (SWIZZLE_128B, no multicast).
+//               two-stage ring (SWIZZLE_128B; every CTA loads its own tiles).
 //
 // Tensor memory (256 columns): S [0,128) O [128,192) P [192,256).
 #pragma once

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the attention kernels use:
-// mbarriers, TMA tiled loads (cp.async.bulk.tensor, no multicast), tensor memory
+// mbarriers, TMA tiled loads (cp.async.bulk.tensor, one CTA per load), tensor memory
 // (tcgen05.alloc / ld / st) and the 5th-generation tensor-core MMA (tcgen05.mma).
 //
 // Every wait in this file is bounded: after roughly two seconds without progress a
@@ -106,7 +106,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // ----------------------------------------------------------------------------------------
-// TMA: tiled 4-D load global -> shared, completion on an mbarrier. No multicast.
+// TMA: tiled 4-D load global -> shared, completion on an mbarrier (CTA-local).
 // ----------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
