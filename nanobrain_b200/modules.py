@@ -1,5 +1,5 @@
-"""Host-side mirror of the reference's ``Attention`` block with the SDPA call swapped for the
-B200 operator.
+"""Host-side mirror of the reference's ``Attention`` and ``Block`` with the SDPA call swapped for
+the B200 operator.
 
 ``Attention`` keeps the reference's constructor arguments, parameter names (``q``, ``k``, ``v``,
 ``proj``: checkpoints load unchanged, cf. ``src/nanobrain/misc.py:343``) and dense behaviour
@@ -80,3 +80,39 @@ class Attention(nn.Module):
             v = self.v(src).view(src.shape[0], heads, hd)
             y = sdpa_varlen(q, k, v, cu_seqlens, cu_k, max_seqlen, max_k).reshape(t, dim)
         return self.proj(y)
+
+
+class Mlp(nn.Module):
+    """Token-wise MLP; same parameters as ``nanobrain.modules.Mlp`` (``modules.py:68-85``)."""
+
+    def __init__(self, dim: int, mlp_ratio: float = 4, bias: bool = False) -> None:
+        super().__init__()
+        hidden = int(dim * mlp_ratio)
+        self.fc1 = nn.Linear(dim, hidden, bias=bias)
+        self.act = nn.GELU()
+        self.fc2 = nn.Linear(hidden, dim, bias=bias)
+
+    def forward(self, x: Tensor) -> Tensor:
+        return self.fc2(self.act(self.fc1(x)))
+
+
+class Block(nn.Module):
+    """Pre-norm residual block, drop-in for ``nanobrain.modules.Block`` (``modules.py:92-131``,
+    stochastic depth 0 as in ``default_pretrain.yaml:36``). ``cu_seqlens`` / ``max_seqlen`` are
+    passed through to the attention, so the same block serves dense ``[B, N, dim]`` and packed
+    ``[T, dim]`` tokens (LayerNorm and the MLP are token-wise)."""
+
+    def __init__(self, dim: int, num_heads: int, qkv_bias: bool = False, proj_bias: bool = False,
+                 context_dim: Optional[int] = None, mlp_ratio: float = 4) -> None:
+        super().__init__()
+        self.norm1 = nn.LayerNorm(dim, eps=1e-6)
+        self.attn = Attention(dim, num_heads, qkv_bias=qkv_bias, proj_bias=proj_bias, context_dim=context_dim)
+        self.drop_path1 = nn.Identity()
+        self.norm2 = nn.LayerNorm(dim, eps=1e-6)
+        self.mlp = Mlp(dim, mlp_ratio=mlp_ratio, bias=proj_bias)
+        self.drop_path2 = nn.Identity()
+
+    def forward(self, x: Tensor, context: Optional[Tensor] = None, cu_seqlens: Optional[Tensor] = None,
+                max_seqlen: Optional[int] = None) -> Tensor:
+        x = x + self.attn(self.norm1(x), context=context, cu_seqlens=cu_seqlens, max_seqlen=max_seqlen)
+        return x + self.mlp(self.norm2(x))

@@ -299,6 +299,43 @@ sdpa_varlen_fwd.register_autograd(_varlen_backward, setup_context=_varlen_setup)
 
 
 # ------------------------------------------------------------------------------------------
+# FLOP formulas: the reference measures TFLOP/s with ``FlopCounterMode`` over one forward +
+# backward (``src/nanobrain/train.py:414-432``); a custom op is invisible to it unless a formula
+# is registered. Same convention as torch's own SDPA formulas: 2 GEMMs forward, 5 backward.
+# ------------------------------------------------------------------------------------------
+def _pair_sum(cu_q: Tensor, cu_k: Tensor) -> int:
+    lq = (cu_q[1:] - cu_q[:-1]).to(torch.int64)
+    lk = (cu_k[1:] - cu_k[:-1]).to(torch.int64)
+    return int((lq * lk).sum().item())
+
+
+def _register_flop_formulas() -> None:
+    from torch.utils.flop_counter import register_flop_formula
+
+    @register_flop_formula(torch.ops.nanobrain_b200.sdpa_fwd)
+    def _(q_shape, k_shape, v_shape, scale, *args, out_shape=None, **kwargs) -> int:
+        b, h, lq, d = q_shape
+        return 4 * b * h * lq * k_shape[2] * d
+
+    @register_flop_formula(torch.ops.nanobrain_b200.sdpa_bwd)
+    def _(d_out_shape, q_shape, k_shape, *args, out_shape=None, **kwargs) -> int:
+        b, h, lq, d = q_shape
+        return 10 * b * h * lq * k_shape[2] * d
+
+    # The varlen formulas need the lengths, i.e. tensor values: get_raw=True hands over the tensors.
+    @register_flop_formula(torch.ops.nanobrain_b200.sdpa_varlen_fwd, get_raw=True)
+    def _(q, k, v, cu_q, cu_k, *args, out_val=None, **kwargs) -> int:
+        return 4 * q.shape[1] * q.shape[2] * _pair_sum(cu_q, cu_k)
+
+    @register_flop_formula(torch.ops.nanobrain_b200.sdpa_varlen_bwd, get_raw=True)
+    def _(d_out, q, k, v, out, lse, cu_q, cu_k, *args, out_val=None, **kwargs) -> int:
+        return 10 * q.shape[1] * q.shape[2] * _pair_sum(cu_q, cu_k)
+
+
+_register_flop_formulas()
+
+
+# ------------------------------------------------------------------------------------------
 # Public functions
 # ------------------------------------------------------------------------------------------
 def sdpa(

@@ -224,3 +224,71 @@ def test_opcheck():
     cu = torch.tensor([0, 30, 70], dtype=torch.int32, device=DEV)
     torch.library.opcheck(ops.sdpa_varlen_fwd, (t, t, t, cu, cu, 40, 40, 0.125),
                           test_utils=("test_schema", "test_faketensor"))
+
+
+def test_packed_blocks_match_dense_blocks_per_sequence():
+    # the packed-token encoder path: Blocks over [T, dim] tokens + cu_seqlens equal the same Blocks
+    # run on every sequence alone (dense path), forward and parameter gradients
+    from nanobrain_b200 import token_prep as T
+
+    torch.manual_seed(0)
+    blocks = torch.nn.ModuleList([modules.Block(128, 2, qkv_bias=True, proj_bias=True) for _ in range(2)]).to(DEV)
+    lengths = torch.tensor([40, 129, 77])
+    cu = T.cu_seqlens_from_counts(lengths).to(DEV)
+    x = torch.randn(int(lengths.sum()), 128, device=DEV)
+
+    def run(packed: bool):
+        for p in blocks.parameters():
+            p.grad = None
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            if packed:
+                y = x
+                for blk in blocks:
+                    y = blk(y, cu_seqlens=cu, max_seqlen=int(lengths.max()))
+            else:
+                outs = []
+                for i in range(len(lengths)):
+                    y = x[int(cu[i]):int(cu[i + 1])][None]
+                    for blk in blocks:
+                        y = blk(y)
+                    outs.append(y[0])
+                y = torch.cat(outs)
+        y.float().square().mean().backward()
+        return y.detach().float(), [p.grad.detach().float().clone() for p in blocks.parameters()]
+
+    y_p, g_p = run(True)
+    y_d, g_d = run(False)
+    ops.check_status()
+    assert (y_p - y_d).abs().max() < 3e-2 * y_d.abs().max()
+    for a, b in zip(g_p, g_d):
+        assert (a - b).abs().max() <= 3e-2 * max(b.abs().max().item(), 1e-3)
+
+
+def test_flop_counter_sees_the_custom_ops():
+    # the reference's TFLOP/s meter runs one fwd+bwd under FlopCounterMode (train.py:414-432)
+    from torch.utils.flop_counter import FlopCounterMode
+
+    q = torch.randn(2, 3, 100, 64, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    with FlopCounterMode(display=False) as fc:
+        nanobrain_b200.sdpa(q, q, q).sum().backward()
+    assert fc.get_total_flops() == 14 * 2 * 3 * 64 * 100 * 100
+    lengths = torch.tensor([30, 70])
+    cu = W.cu_seqlens_from_lengths(lengths).to(DEV)
+    t = torch.randn(100, 3, 64, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    with FlopCounterMode(display=False) as fc:
+        nanobrain_b200.sdpa_varlen(t, t, t, cu, cu, 70, 70).sum().backward()
+    assert fc.get_total_flops() == W.attention_flops(lengths, lengths, 3)
+
+
+def test_attention_module_compiles_without_graph_breaks():
+    # the reference compiles the model in place (train.py:100-102)
+    attn = modules.Attention(128, 2).to(DEV)
+    x = torch.randn(2, 60, 128, device=DEV, requires_grad=True)
+    compiled = torch.compile(attn, fullgraph=True)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y_c = compiled(x)
+        y_e = attn(x)
+    y_c.float().sum().backward()
+    ops.check_status()
+    assert (y_c.float() - y_e.float()).abs().max() < 2e-2
+    assert torch.isfinite(x.grad).all()
