@@ -402,6 +402,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const bool row_valid = (k_row0 + krow_in_tile) < lk;
       const bool partial = (k_row0 + kTile) > lk;
       const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
+      // Iteration that visits the last, ragged query tile (-1 if the length is a multiple of the tile).
+      const int j_ragged = (lq % kTile) != 0 ? (n_q - 1 - kt % n_q + n_q) % n_q : -1;
       for (int j = 0; j < n_q; ++j) {
         const int qs = j % kBwdStages;
         const float4* lse4 = reinterpret_cast<const float4*>(sLse + qs * kTile + 64 * w);   // -lse (log2)
@@ -443,6 +445,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           // Key rows past the end of the sequence must not contribute to dQ.
 #pragma unroll
           for (int i = 0; i < 32; ++i) pf[i] = 0ull;
+        }
+        if (j == j_ragged) {
+          // Query columns past the end of the sequence: the hardware exponential already gave 0 for
+          // their -inf argument, the polynomial's clamp gave 2^-126. Make all of them exactly 0, so
+          // that nothing at all is added to the dQ rows of the next packed sequence.
+          const int valid = lq - (n_q - 1) * kTile - 64 * w;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float a0, a1;
+            unpack_f32x2(pf[i], a0, a1);
+            pf[i] = pack_f32x2(2 * i < valid ? a0 : 0.f, 2 * i + 1 < valid ? a1 : 0.f);
+          }
         }
         if (j > 0) {
           if (!pt_ok) mbar_wait(bar(kBarPtFree), (j - 1) & 1, &abort_flag, p.status);

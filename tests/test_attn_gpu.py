@@ -292,3 +292,31 @@ def test_attention_module_compiles_without_graph_breaks():
     ops.check_status()
     assert (y_c.float() - y_e.float()).abs().max() < 2e-2
     assert torch.isfinite(x.grad).all()
+
+
+def test_empty_sequences_inside_a_packed_batch():
+    # a sequence of length 0 owns no rows: its neighbours are unaffected and nothing hangs
+    lengths = torch.tensor([70, 0, 129, 0])
+    got, want, _ = run_varlen(lengths, heads=2, seed=23)
+    close("out", got[0], want[0]), close("dq", got[1], want[2]), close("dk", got[2], want[3]), close("dv", got[3], want[4])
+
+
+def test_queries_without_keys_and_keys_without_queries():
+    # cross lengths where one side of a sequence is empty: queries with no keys get zero output and
+    # -inf LSE; keys with no queries get zero gradients
+    lq, lk = torch.tensor([40, 50, 0]), torch.tensor([60, 0, 30])
+    cu_q, cu_k = W.cu_seqlens_from_lengths(lq).to(DEV), W.cu_seqlens_from_lengths(lk).to(DEV)
+    g = torch.Generator().manual_seed(29)
+    q = torch.randn(90, 2, 64, generator=g).to(DEV, torch.bfloat16).requires_grad_(True)
+    k = torch.randn(90, 2, 64, generator=g).to(DEV, torch.bfloat16).requires_grad_(True)
+    v = torch.randn(90, 2, 64, generator=g).to(DEV, torch.bfloat16).requires_grad_(True)
+    out, lse = ops.sdpa_varlen_fwd(q, k, v, cu_q, cu_k, 50, 60, 0.125)
+    out.float().sum().backward()
+    ops.check_status()
+    assert torch.all(out[40:90] == 0) and torch.all(torch.isinf(lse[:, 40:90]))
+    assert torch.isfinite(out[:40].float()).all()
+    assert torch.all(k.grad[60:90] == 0) and torch.all(v.grad[60:90] == 0)  # keys of the query-less sequence
+    assert torch.all(q.grad[40:90] == 0)                                     # queries of the key-less sequence
+    want = O.sdpa_fwd_bwd(q[:40].detach().float().cpu().numpy().swapaxes(0, 1), k[:60].detach().float().cpu().numpy().swapaxes(0, 1),
+                          v[:60].detach().float().cpu().numpy().swapaxes(0, 1), np.ones((2, 40, 64)), dtype=np.float32)
+    close("out", out[:40].transpose(0, 1), want[0]), close("dk", k.grad[:60].transpose(0, 1), want[3])
