@@ -201,7 +201,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
 
-  if (tid == 0) {
+  // The producer's own thread initialises the barriers, so it can request K, V and the first Q/dO
+  // tiles at once; the other threads meet the barriers only after the __syncthreads below.
+  if (tid == 16 * 32) {
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_v);
+    tma_prefetch_desc(&tmap_do);
     abort_flag = 0;
     for (int i = 0; i < kBwdNumBars; ++i) {
       uint32_t count = 1;
@@ -214,6 +220,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_init(bar(i), count);
     }
     fence_mbar_init();
+    if (n_q > 0) {
+      const int jt0 = kt % n_q;
+      mbar_arrive_expect_tx(bar(kBarKvFull), 2 * kTileBytes);
+      tma_load_4d(sK, &tmap_k, bar(kBarKvFull), 0, k_begin + k_row0, h, bcoord);
+      tma_load_4d(sV, &tmap_v, bar(kBarKvFull), 0, k_begin + k_row0, h, bcoord);
+      mbar_arrive_expect_tx(bar(kBarQdoFull), 2 * kTileBytes);
+      tma_load_4d(sQ(0), &tmap_q, bar(kBarQdoFull), 0, q_begin + jt0 * kTile, h, bcoord);
+      tma_load_4d(sDO(0), &tmap_do, bar(kBarQdoFull), 0, q_begin + jt0 * kTile, h, bcoord);
+    }
   }
   if (warp == 8) {
     tmem_alloc(smem_u32(&tmem_base_slot), kBwdTmemCols);
@@ -236,23 +251,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // ---------------- TMA producer + LSE/delta staging (warp 16; 17-19 idle) ----------------
       setmaxnreg_dec<kBwdLoaderRegs>();
       if (warp == 16) {
-      if (lane == 0) {
-        tma_prefetch_desc(&tmap_q);
-        tma_prefetch_desc(&tmap_k);
-        tma_prefetch_desc(&tmap_v);
-        tma_prefetch_desc(&tmap_do);
-        mbar_arrive_expect_tx(bar(kBarKvFull), 2 * kTileBytes);
-        tma_load_4d(sK, &tmap_k, bar(kBarKvFull), 0, k_begin + k_row0, h, bcoord);
-        tma_load_4d(sV, &tmap_v, bar(kBarKvFull), 0, k_begin + k_row0, h, bcoord);
-      }
       for (int j = 0; j < n_q; ++j) {
         const int qs = j % kBwdStages;
         const int jt = (j + kt) % n_q;  // staggered start: concurrent CTAs touch different dQ tiles
         if (j >= kBwdStages && lane == 0)
           mbar_wait(bar(kBarQdoEmpty + qs), ((j / kBwdStages) - 1) & 1, &abort_flag, p.status);
         __syncwarp();
-        // TMA first, so that its latency overlaps the LSE/delta loads below.
-        if (lane == 0) {
+        // TMA first, so that its latency overlaps the LSE/delta loads below (tile 0 is already on its way).
+        if (lane == 0 && j > 0) {
           mbar_arrive_expect_tx(bar(kBarQdoFull + qs), 2 * kTileBytes);
           tma_load_4d(sQ(qs), &tmap_q, bar(kBarQdoFull + qs), 0, q_begin + jt * kTile, h, bcoord);
           tma_load_4d(sDO(qs), &tmap_do, bar(kBarQdoFull + qs), 0, q_begin + jt * kTile, h, bcoord);

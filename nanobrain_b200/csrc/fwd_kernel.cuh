@@ -118,10 +118,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const uint32_t bar_s_full = bar0 + 8 * 7, bar_s_free = bar0 + 8 * 8;
   const uint32_t bar_p_full = bar0 + 8 * 9, bar_pv_done = bar0 + 8 * 10;
 
-  if (tid == 0) {
+  // The producer's own thread initialises the barriers, so it can start the first loads (Q and both
+  // K/V stages) at once; the other threads meet the barriers only after the __syncthreads below.
+  if (tid == 5 * 32) {
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
     abort_flag = 0;
     for (int i = 0; i < 11; ++i) mbar_init(bar0 + 8 * i, (i == 8 || i == 9) ? 4 : 1);  // s_free, p_full: per warp
     fence_mbar_init();
+    if (n_kv > 0) {
+      mbar_arrive_expect_tx(bar_q_full, kTileBytes);
+      tma_load_4d(sQ, &tmap_q, bar_q_full, 0, q_begin + q_row0, h, bcoord);
+      for (int i = 0; i < kFwdStages && i < n_kv; ++i) {
+        mbar_arrive_expect_tx(bar_k_full(i), kTileBytes);
+        tma_load_4d(sK(i), &tmap_k, bar_k_full(i), 0, k_begin + i * kTile, h, bcoord);
+        mbar_arrive_expect_tx(bar_v_full(i), kTileBytes);
+        tma_load_4d(sV(i), &tmap_v, bar_v_full(i), 0, k_begin + i * kTile, h, bcoord);
+      }
+    }
   }
   if (warp == 4) {
     tmem_alloc(smem_u32(&tmem_base_slot), kFwdTmemCols);
@@ -137,14 +152,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     if (warp == 5) {
       // ---------------- TMA producer ----------------
       if (elect_one()) {
-        tma_prefetch_desc(&tmap_q);
-        tma_prefetch_desc(&tmap_k);
-        tma_prefetch_desc(&tmap_v);
-        mbar_arrive_expect_tx(bar_q_full, kTileBytes);
-        tma_load_4d(sQ, &tmap_q, bar_q_full, 0, q_begin + q_row0, h, bcoord);
-        for (int i = 0; i < n_kv; ++i) {
+        for (int i = kFwdStages; i < n_kv; ++i) {  // the first tiles were requested at start-up
           const int s = i % kFwdStages;
-          if (i >= kFwdStages) mbar_wait(bar_kv_empty(s), ((i / kFwdStages) - 1) & 1, &abort_flag, p.status);
+          mbar_wait(bar_kv_empty(s), ((i / kFwdStages) - 1) & 1, &abort_flag, p.status);
           mbar_arrive_expect_tx(bar_k_full(s), kTileBytes);
           tma_load_4d(sK(s), &tmap_k, bar_k_full(s), 0, k_begin + i * kTile, h, bcoord);
           mbar_arrive_expect_tx(bar_v_full(s), kTileBytes);
