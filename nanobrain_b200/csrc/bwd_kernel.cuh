@@ -254,27 +254,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       for (int j = 0; j < n_q; ++j) {
         const int qs = j % kBwdStages;
         const int jt = (j + kt) % n_q;  // staggered start: concurrent CTAs touch different dQ tiles
+        // The tile's LSE/delta rows are requested before the wait for a free stage, so that this
+        // latency does not sit between a stage becoming free and becoming full again. They are
+        // staged negated: -lse in the log2 domain and -delta. Rows past the end of the sequence get
+        // -lse = -inf, which makes their P^T column 0.
+        float l2[4], dl[4];
+#pragma unroll
+        for (int r4 = 0; r4 < 4; ++r4) {
+          const int r = jt * kTile + r4 * 32 + lane;
+          l2[r4] = -INFINITY, dl[r4] = 0.f;
+          if (r < lq) {
+            l2[r4] = p.lse[stat_base + r] * -1.4426950408889634f;
+            dl[r4] = -p.delta[stat_base + r];
+          }
+        }
         if (j >= kBwdStages && lane == 0)
           mbar_wait(bar(kBarQdoEmpty + qs), ((j / kBwdStages) - 1) & 1, &abort_flag, p.status);
         __syncwarp();
-        // TMA first, so that its latency overlaps the LSE/delta loads below (tile 0 is already on its way).
-        if (lane == 0 && j > 0) {
+        if (lane == 0 && j > 0) {  // tile 0 is already on its way
           mbar_arrive_expect_tx(bar(kBarQdoFull + qs), 2 * kTileBytes);
           tma_load_4d(sQ(qs), &tmap_q, bar(kBarQdoFull + qs), 0, q_begin + jt * kTile, h, bcoord);
           tma_load_4d(sDO(qs), &tmap_do, bar(kBarQdoFull + qs), 0, q_begin + jt * kTile, h, bcoord);
         }
-        // Staged negated: -lse in the log2 domain and -delta. Rows past the end of the sequence get
-        // -lse = -inf, which makes their P^T column exactly 0.
 #pragma unroll
         for (int r4 = 0; r4 < 4; ++r4) {
-          const int r = jt * kTile + r4 * 32 + lane;
-          float l2 = -INFINITY, dl = 0.f;
-          if (r < lq) {
-            l2 = p.lse[stat_base + r] * -1.4426950408889634f;
-            dl = -p.delta[stat_base + r];
-          }
-          sLse[qs * kTile + r4 * 32 + lane] = l2;
-          sDelta[qs * kTile + r4 * 32 + lane] = dl;
+          sLse[qs * kTile + r4 * 32 + lane] = l2[r4];
+          sDelta[qs * kTile + r4 * 32 + lane] = dl[r4];
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(kBarQdoFull + qs));
