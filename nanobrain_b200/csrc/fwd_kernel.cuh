@@ -74,7 +74,11 @@ __device__ __forceinline__ void chunk_exp(const uint32_t (&r)[32], uint64_t scal
     float x0, x1;
     unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), scale2, neg_m2),
                  x0, x1);
-    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+    float p0, p1;
+    // One pair in eight takes the polynomial on the FMA pipe; the other exponentials keep the MUFU
+    // unit (16 results per clock per SM) as busy as the rest of the loop allows.
+    if ((j & 7) == 7) unpack_f32x2(exp2_poly_f32x2(pack_f32x2(x0, x1)), p0, p1);
+    else p0 = fast_exp2(x0), p1 = fast_exp2(x1);
     if (j & 1) l23 = add_f32x2(l23, pack_f32x2(p0, p1)); else l01 = add_f32x2(l01, pack_f32x2(p0, p1));
     pk[j] = pack_bf16(p0, p1);
   }
