@@ -41,7 +41,7 @@ NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_bwd_kernel launch, from the ncu capture
 # summarised in profiles/attn_kernels_vitb_encoder_varlen.md (only known for that workload).
-NCU_DRAM_BYTES_BWD_MAIN = {"vitb_encoder_varlen": 365.3e6}
+NCU_DRAM_BYTES_BWD_MAIN = {"vitb_encoder_varlen": 364.6e6}
 
 
 def parse_args():
