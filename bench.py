@@ -11,8 +11,8 @@ rank's device time. ``--global-batch B`` shards one global batch of B sequences 
 instead (strong scaling).
 
 Rank 0 prints ONE JSON line. ``value`` is device-resident throughput through the C ABI;
-``e2e`` goes through the public torch op with host buffers (H2D of Q, K, V, dO and D2H of O, dQ,
-dK, dV inside the timed region); ``roofline`` times the dominant kernel (backward main) with CUDA
+``e2e`` goes through the package's host-buffer entry (``nanobrain_b200.HostPipeline``: H2D of Q, K,
+V, dO and D2H of O, dQ, dK, dV inside the timed region, pipelined with the kernels); ``roofline`` times the dominant kernel (backward main) with CUDA
 events recorded around it inside the timed region; ``cpu_baseline`` times the reference's own CPU
 path (torch CPU SDPA, fp32) on this machine's host cores.
 """
@@ -54,6 +54,7 @@ def parse_args():
     ap.add_argument("--global-batch", type=int, default=0,
                     help="shard one global batch of this many sequences across ranks (strong scaling)")
     ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--e2e-groups", type=int, default=8, help="sequence groups of the host-buffer pipeline")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     return ap.parse_args()
 
@@ -309,23 +310,19 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     if int(status.item()) != 0:
         raise RuntimeError("kernel reported a device status during the timed region")
 
-    # End to end through the public op with host buffers.
+    # End to end with host buffers: pinned inputs in, pinned results out, through the package's
+    # host-buffer entry (nanobrain_b200.HostPipeline: copies and kernels pipelined over groups of
+    # sequences). Every step moves all four inputs to the device and all four results back.
     e2e_steps = max(1, min(args.e2e_steps, args.steps))
-    host_out = [torch.empty_like(host[0]) for _ in range(4)]
-    dev_in = [torch.empty_like(q) for _ in range(4)]
+    host_out = [torch.empty_like(host[0]).pin_memory() for _ in range(4)]
+    pipe = nanobrain_b200.HostPipeline(lengths.tolist(), heads, dev, groups=args.e2e_groups)
 
     def e2e_step():
-        for d, h in zip(dev_in, host):
-            d.copy_(h, non_blocking=True)
-        qq, kk, vv = (t.detach().requires_grad_(True) for t in dev_in[:3])
-        o = nanobrain_b200.sdpa_varlen(qq, kk, vv, cu, cu, max_len, max_len)
-        o.backward(dev_in[3])
-        for h, d in zip(host_out, (o.detach(), qq.grad, kk.grad, vv.grad)):
-            h.copy_(d, non_blocking=True)
+        pipe.run(*host, *host_out)
 
     for _ in range(2):
         e2e_step()
-    torch.cuda.synchronize()
+    pipe.check_status()
     if world > 1:
         dist.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -335,7 +332,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     e1.record(stream)
     torch.cuda.synchronize()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
-    ops.check_status(dev)
+    pipe.check_status()
+    # The pipelined path must give what the device-resident path gave (same kernels, same inputs).
+    if not (torch.equal(host_out[0], out.cpu()) and torch.equal(host_out[2], dk.cpu())):
+        raise RuntimeError("host pipeline results differ from the device-resident results")
 
     # Max over ranks of the device times; sums of the work.
     stats = torch.tensor([elapsed_ms, e2e_ms, float(flops_step), float(total)], dtype=torch.float64, device=dev)

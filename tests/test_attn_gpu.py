@@ -320,3 +320,26 @@ def test_queries_without_keys_and_keys_without_queries():
     want = O.sdpa_fwd_bwd(q[:40].detach().float().cpu().numpy().swapaxes(0, 1), k[:60].detach().float().cpu().numpy().swapaxes(0, 1),
                           v[:60].detach().float().cpu().numpy().swapaxes(0, 1), np.ones((2, 40, 64)), dtype=np.float32)
     close("out", out[:40].transpose(0, 1), want[0]), close("dk", k.grad[:60].transpose(0, 1), want[3])
+
+
+def test_host_pipeline_matches_the_device_resident_op():
+    # pinned host tensors in, pinned host tensors out, copies and kernels pipelined over sequence groups
+    lengths = torch.tensor([130, 64, 1, 300, 77, 128, 255])
+    heads = 3
+    host_in = [t.to(torch.bfloat16).pin_memory() for t in W.make_packed_inputs(lengths, heads, seed=31)]
+    host_out = [torch.empty_like(host_in[0]).pin_memory() for _ in range(4)]
+    pipe = nanobrain_b200.HostPipeline(lengths.tolist(), heads, torch.device(DEV), groups=3)
+    assert len(pipe.groups) == 3
+    for _ in range(2):  # a second run reuses every buffer
+        pipe.run(*host_in, *host_out)
+    pipe.check_status()
+    cu = W.cu_seqlens_from_lengths(lengths).to(DEV)
+    q, k, v = (t.to(DEV).requires_grad_(True) for t in host_in[:3])
+    out = nanobrain_b200.sdpa_varlen(q, k, v, cu, cu, int(lengths.max()), int(lengths.max()))
+    out.backward(host_in[3].to(DEV))
+    ops.check_status()
+    assert torch.equal(host_out[0], out.detach().cpu())   # forward is deterministic
+    assert torch.equal(host_out[2], k.grad.cpu()) and torch.equal(host_out[3], v.grad.cpu())
+    close("dq", host_out[1], q.grad.float().cpu().numpy())  # fp32 add-reductions arrive in any order
+    with pytest.raises(RuntimeError, match="pinned"):
+        pipe.run(*[t.clone() for t in host_in], *host_out)

@@ -6,6 +6,7 @@ import torch
 
 import nanobrain_b200
 from nanobrain_b200 import modules, ops
+from nanobrain_b200 import workloads as W
 
 
 def test_unsupported_arguments_raise_instead_of_falling_back():
@@ -62,3 +63,24 @@ def test_attention_module_mirrors_reference_parameters(golden_dir):
         modules.Attention(dim=128, num_heads=4)  # head_dim 32
     with pytest.raises(ValueError):
         modules.Attention(dim=128, num_heads=2, causal=True)
+
+
+def test_split_sequences_covers_every_sequence_once_and_balances_tokens():
+    from nanobrain_b200.host_pipeline import split_sequences
+
+    lengths = [int(x) for x in W.draw_lengths(W.WORKLOADS["vitb_encoder_varlen"])]
+    for groups in (1, 3, 8, 32, 100):
+        runs = split_sequences(lengths, groups)
+        assert [i for r in runs for i in r] == list(range(len(lengths)))  # consecutive, complete, no overlap
+        assert 1 <= len(runs) <= min(groups, len(lengths)) and all(len(r) > 0 for r in runs)
+    tokens = [sum(lengths[i] for i in r) for r in split_sequences(lengths, 8)]
+    assert max(tokens) <= 1.5 * sum(lengths) / 8
+    assert split_sequences([5], 4) == [range(0, 1)]
+    assert [list(r) for r in split_sequences([1, 1, 1], 3)] == [[0], [1], [2]]
+
+
+def test_host_pipeline_refuses_a_cpu_device():
+    from nanobrain_b200 import HostPipeline
+
+    with pytest.raises(RuntimeError, match="CUDA"):
+        HostPipeline([10, 20], 2, torch.device("cpu"))
