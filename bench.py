@@ -312,7 +312,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     # End to end with host buffers: pinned inputs in, pinned results out, through the package's
     # host-buffer entry (nanobrain_b200.HostPipeline: copies and kernels pipelined over groups of
-    # sequences). Every step moves all four inputs to the device and all four results back.
+    # sequences, successive steps overlapping like a prefetching input pipeline). Every step moves
+    # all four inputs to the device and all four results back.
     e2e_steps = max(1, min(args.e2e_steps, args.steps))
     host_out = [torch.empty_like(host[0]).pin_memory() for _ in range(4)]
     pipe = nanobrain_b200.HostPipeline(lengths.tolist(), heads, dev, groups=args.e2e_groups)
@@ -329,6 +330,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     e0.record(stream)
     for _ in range(e2e_steps):
         e2e_step()
+    pipe.wait()  # the timed region ends when the last step's results are in host memory
     e1.record(stream)
     torch.cuda.synchronize()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps

@@ -12,8 +12,10 @@ independent problems), and three CUDA streams run the groups as a pipeline
     copy-out stream: O, dQ, dK, dV of group c-1  device -> host
 
 so that the two PCIe directions and the GPU work at the same time. All device memory is allocated
-once in the constructor; ``run`` allocates nothing and returns after queueing the work, with the
-caller's current stream made to wait for the last copy-out.
+once in the constructor; ``run`` allocates nothing and only queues work, ``wait`` makes the caller's
+current stream wait for everything queued so far. Successive ``run`` calls overlap as well (the
+copy-in of the next step runs under the kernels and the copy-out of the current one); events per
+group keep a step from overwriting device buffers the previous step still uses.
 """
 
 from __future__ import annotations
@@ -100,7 +102,8 @@ class HostPipeline:
             bwd = _lib.BwdArgs(sh, d(q), d(k), d(v), d(o), d(g), d(dq), d(dk), d(dv), lse.data_ptr(),
                                ws.data_ptr(), ws_bytes, self.status.data_ptr(), None, None)
             self.groups.append({"slice": sl, "fwd": fwd, "bwd": bwd, "keep": (cu, lse, ws),
-                                "ev_in": torch.cuda.Event(), "ev_done": torch.cuda.Event()})
+                                "ev_in": torch.cuda.Event(), "ev_done": torch.cuda.Event(),
+                                "ev_out": torch.cuda.Event()})
 
     @staticmethod
     def _desc(t: Tensor) -> _lib.Tensor:
@@ -120,24 +123,24 @@ class HostPipeline:
     def run(self, q: Tensor, k: Tensor, v: Tensor, d_out: Tensor, out: Tensor, dq: Tensor, dk: Tensor,
             dv: Tensor) -> None:
         """Queue one forward + backward. Inputs ``q, k, v, d_out`` and outputs ``out, dq, dk, dv`` are
-        pinned host tensors; the results are complete once the caller's current stream has reached
-        this point (``torch.cuda.current_stream().synchronize()``)."""
+        pinned host tensors. The inputs must stay unchanged, and the outputs are not complete, until
+        ``wait()`` has been called and the caller's stream has reached that point."""
         self._check_host((q, k, v, d_out), "inputs")
         self._check_host((out, dq, dk, dv), "outputs")
-        main = torch.cuda.current_stream(self.device)
-        # Everything the caller queued before (an earlier run's copies included) comes first.
-        for s in (self.s_in, self.s_compute, self.s_out):
-            s.wait_stream(main)
+        # What the caller queued before comes first; an earlier run is ordered by the events below.
+        self.s_in.wait_stream(torch.cuda.current_stream(self.device))
         host_in, host_out = (q, k, v, d_out), (out, dq, dk, dv)
         sptr = C.c_void_p(self.s_compute.cuda_stream)
         with torch.cuda.device(self.device):
             for grp in self.groups:
                 sl = grp["slice"]
+                self.s_in.wait_event(grp["ev_done"])      # the previous run has finished with these inputs
                 with torch.cuda.stream(self.s_in):
                     for d, h in zip(self.dev_in, host_in):
                         d[sl].copy_(h[sl], non_blocking=True)
                     grp["ev_in"].record(self.s_in)
                 self.s_compute.wait_event(grp["ev_in"])
+                self.s_compute.wait_event(grp["ev_out"])  # the previous run's results have left the device
                 with torch.cuda.stream(self.s_compute):
                     _lib.check(self.lib.nb_attn_fwd(C.byref(grp["fwd"]), sptr), "nb_attn_fwd")
                     _lib.check(self.lib.nb_attn_bwd(C.byref(grp["bwd"]), sptr), "nb_attn_bwd")
@@ -146,12 +149,17 @@ class HostPipeline:
                 with torch.cuda.stream(self.s_out):
                     for h, d in zip(host_out, self.dev_out):
                         h[sl].copy_(d[sl], non_blocking=True)
-        main.wait_stream(self.s_out)
-        main.wait_stream(self.s_compute)
-        main.wait_stream(self.s_in)
+                    grp["ev_out"].record(self.s_out)
+
+    def wait(self) -> None:
+        """Make the caller's current stream wait for every run queued so far."""
+        main = torch.cuda.current_stream(self.device)
+        for s in (self.s_out, self.s_compute, self.s_in):
+            main.wait_stream(s)
 
     def check_status(self) -> None:
         """Synchronise and raise if a kernel reported a timed-out wait."""
+        self.wait()
         torch.cuda.synchronize(self.device)
         code = int(self.status.item())
         if code != 0:
