@@ -1,8 +1,8 @@
 """Generates the golden fixtures in this directory from the reference's own code path.
 
-Run in the build container, where the reference source tree is mounted read-only:
+Run where a checkout of the reference project is available, giving its root directory:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to the nanobrain checkout>
 
 Two fixtures are written (fp32, CPU):
 
@@ -87,7 +87,9 @@ def make_attention_module(ref_root: Path):
 
 
 if __name__ == "__main__":
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path to the nanobrain checkout>")
+    root = Path(sys.argv[1])
     make_sdpa_small()
     make_attention_module(root)
     print("wrote", sorted(p.name for p in HERE.glob("*.npz")))
