@@ -343,3 +343,39 @@ def test_host_pipeline_matches_the_device_resident_op():
     close("dq", host_out[1], q.grad.float().cpu().numpy())  # fp32 add-reductions arrive in any order
     with pytest.raises(RuntimeError, match="pinned"):
         pipe.run(*[t.clone() for t in host_in], *host_out)
+
+
+def test_large_varlen_config_full_size_by_properties():
+    # The 20x24x20-grid encoder case (B=16, H=16, L~U[1700,2140]) at full size. The oracle checks the
+    # shortest and the longest sequence; size-independent properties cover the rest:
+    #  * softmax rows sum to 1: with V = 1 the output is 1 everywhere;
+    #  * dV = P^T dO: with dO = 1, every head's dV summed over a sequence's keys equals its number of queries;
+    #  * softmax is shift-invariant, so dQ and dK vanish when V is constant (dP is constant per row).
+    w = W.WORKLOADS["vitl_encoder_varlen"]
+    lengths = W.draw_lengths(w)
+    heads = w.heads
+    q, k, v, g_out = rounded(*W.make_packed_inputs(lengths, heads, seed=3))
+    cu = W.cu_seqlens_from_lengths(lengths)
+    cud = cu.to(DEV)
+    max_len = int(lengths.max())
+    qd, kd, vd = (t.to(DEV, torch.bfloat16).requires_grad_(True) for t in (q, k, v))
+    out = nanobrain_b200.sdpa_varlen(qd, kd, vd, cud, cud, max_len, max_len)
+    out.backward(g_out.to(DEV, torch.bfloat16))
+    ops.check_status()
+    for i in (int(lengths.argmin()), int(lengths.argmax())):
+        a, b = int(cu[i]), int(cu[i + 1])
+        sl = lambda t: t[a:b].transpose(0, 1).numpy()
+        want = O.sdpa_fwd_bwd(sl(q), sl(k), sl(v), sl(g_out), dtype=np.float32)
+        close("out", out[a:b].transpose(0, 1), want[0]), close("dq", qd.grad[a:b].transpose(0, 1), want[2])
+        close("dk", kd.grad[a:b].transpose(0, 1), want[3]), close("dv", vd.grad[a:b].transpose(0, 1), want[4])
+    ones = torch.ones_like(vd)
+    q1, k1, v1 = (t.detach().clone().requires_grad_(True) for t in (qd, kd, ones))
+    out1 = nanobrain_b200.sdpa_varlen(q1, k1, v1, cud, cud, max_len, max_len)
+    out1.backward(torch.ones_like(out1))
+    ops.check_status()
+    assert (out1.float() - 1).abs().max() <= 8e-3          # bf16 rounding of a value near 1
+    for i in range(lengths.numel()):
+        a, b = int(cu[i]), int(cu[i + 1])
+        col_sums = v1.grad[a:b].float().sum(0)               # [H, 64]: sum over keys of sum_q P[q, k] = number of queries
+        assert (col_sums / (b - a) - 1).abs().max() <= 2e-2
+    assert q1.grad.float().abs().max() <= 1e-2 and k1.grad.float().abs().max() <= 1e-2
