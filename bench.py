@@ -53,7 +53,7 @@ def parse_args():
     ap.add_argument("--workload", default="vitb_encoder_varlen")
     ap.add_argument("--global-batch", type=int, default=0,
                     help="shard one global batch of this many sequences across ranks (strong scaling)")
-    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--e2e-steps", type=int, default=40)
     ap.add_argument("--e2e-groups", type=int, default=8, help="sequence groups of the host-buffer pipeline")
     ap.add_argument("--skip-cpu-baseline", action="store_true")
     return ap.parse_args()
