@@ -10,7 +10,7 @@ import ctypes as C
 from pathlib import Path
 
 LIB_PATH = Path(__file__).resolve().parent / "libnb_attn.so"
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 # Every symbol include/nb_attn.h declares.
 EXPORTED_SYMBOLS = (
@@ -21,8 +21,23 @@ EXPORTED_SYMBOLS = (
     "nb_attn_abi_version",
     "nb_attn_selftest_mma",
     "nb_attn_bwd_builtin_scratch",
+    "nb_attn_fwd_workspace_bytes",
+    "nb_attn_selftest_wait",
+    "nb_attn_schedule_capacity",
+    "nb_attn_schedule_build",
+    "nb_attn_schedule_host",
 )
 BUILTIN_SCRATCH_ROWS = 65536
+BUILTIN_SCRATCH_ITEMS = 16384
+SCHED_ITEM_INTS = 8   # an nb_attn_sched_item is eight int32: seq, tile, own begin/len, other begin/len, 2 reserved
+
+# Codes a kernel may write to the status word (enum nb_attn_status).
+STATUS_OK, STATUS_WAIT_TIMEOUT, STATUS_BAD_SEQLENS = 0, 1, 2
+STATUS_TEXT = {
+    STATUS_WAIT_TIMEOUT: "a bounded wait inside a kernel gave up; results are garbage",
+    STATUS_BAD_SEQLENS: "cu_seqlens is not a valid packing (offsets decreasing, a sequence longer than "
+                        "max_seqlen, or the last offset beyond the token count); outputs were not written",
+}
 
 
 class Tensor(C.Structure):
@@ -58,6 +73,8 @@ class FwdArgs(C.Structure):
         ("o", Tensor),
         ("lse", C.c_void_p),
         ("status", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
     ]
 
 
@@ -100,7 +117,18 @@ def load() -> C.CDLL:
     lib.nb_attn_strerror.restype = C.c_char_p
     lib.nb_attn_strerror.argtypes = [C.c_int]
     lib.nb_attn_bwd_workspace_bytes.restype = C.c_size_t
-    lib.nb_attn_bwd_workspace_bytes.argtypes = [C.c_int64, C.c_int32, C.c_int32]
+    lib.nb_attn_bwd_workspace_bytes.argtypes = [C.POINTER(Shape)]
+    lib.nb_attn_fwd_workspace_bytes.restype = C.c_size_t
+    lib.nb_attn_fwd_workspace_bytes.argtypes = [C.POINTER(Shape)]
+    lib.nb_attn_selftest_wait.restype = C.c_int
+    lib.nb_attn_selftest_wait.argtypes = [C.c_uint64, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.nb_attn_schedule_capacity.restype = C.c_int64
+    lib.nb_attn_schedule_capacity.argtypes = [C.c_int64, C.c_int32]
+    lib.nb_attn_schedule_build.restype = C.c_int
+    lib.nb_attn_schedule_build.argtypes = [C.POINTER(Shape), C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
+    lib.nb_attn_schedule_host.restype = C.c_int
+    lib.nb_attn_schedule_host.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int64,
+                                          C.c_int64, C.c_int, C.c_void_p, C.c_int64]
     lib.nb_attn_fwd.restype = C.c_int
     lib.nb_attn_fwd.argtypes = [C.POINTER(FwdArgs), C.c_void_p]
     lib.nb_attn_bwd.restype = C.c_int
@@ -114,6 +142,16 @@ def load() -> C.CDLL:
         raise RuntimeError(f"libnb_attn.so has ABI version {got}, this package expects {ABI_VERSION}")
     _lib = lib
     return lib
+
+
+def fwd_workspace_bytes(shape: Shape) -> int:
+    """Scratch bytes ``nb_attn_fwd`` needs for this shape (0 in dense mode)."""
+    return int(load().nb_attn_fwd_workspace_bytes(C.byref(shape)))
+
+
+def bwd_workspace_bytes(shape: Shape) -> int:
+    """Scratch bytes ``nb_attn_bwd`` needs for this shape."""
+    return int(load().nb_attn_bwd_workspace_bytes(C.byref(shape)))
 
 
 def check(code: int, what: str) -> None:

@@ -24,6 +24,15 @@
 //                              LSE/delta rows (warps 17-19 only complete its warpgroup for the
 //                              register re-partitioning).
 //   attn_bwd_epilogue_kernel : dQ = bf16(scale * accumulator). HBM-bound.
+//
+// Packed mode: block 0 of the prologue also builds the scheduler's work list of key tiles
+// (sched_kernel.cuh) and the main kernel's grid runs the whole list once per head. A ragged tile is computed at full
+// width and masked: rows of the NEXT packed sequence that it brings into shared memory are
+// multiplied by exact zeros of P^T / dS^T. For finite data that is exact; if the next sequence's
+// first rows hold Inf or NaN, 0 x Inf makes this sequence's gradients NaN as well (the forward
+// kernel clears such rows and keeps sequences isolated; measured here, clearing them in this
+// kernel cost 7 % of its time, and cutting the MMAs of ragged tiles to their live rows gained
+// nothing, so neither is done).
 #pragma once
 
 #include "fwd_kernel.cuh"
@@ -41,9 +50,11 @@ struct BwdParams {
   float* dq_accum;  // fp32 [total_q][heads][64]
   const int32_t* cu_q;
   const int32_t* cu_k;
+  const SchedItem* items;  // packed mode: work list of key tiles; CTA x runs entry x % n_items for head x / n_items
+  SchedParams sched;      // packed mode: what block 0 of the prologue builds (items == NULL: nothing)
   int32_t batch, heads;
   int32_t lq, lk;
-  int64_t total_q;
+  int64_t total_q, total_k;
   float scale, scale_log2;
   int32_t* status;
 };
@@ -52,6 +63,10 @@ struct BwdParams {
 // Prologue: one quarter-warp (8 lanes x 16 bytes) per (token, head) row.
 // ----------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) attn_bwd_prologue_kernel(const BwdParams p) {
+  __shared__ SchedShared sched_sm;
+  pdl_wait();  // O comes from the forward kernel, dO from whatever ran before this call
+  pdl_launch_dependents();
+  if (blockIdx.x == 0 && p.sched.items != nullptr) sched_build<256>(p.sched, sched_sm);
   const int64_t n_rows = p.total_q * p.heads;
   const int lane8 = threadIdx.x & 7;
   int64_t row = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
@@ -95,6 +110,8 @@ __global__ void __launch_bounds__(256) attn_bwd_prologue_kernel(const BwdParams 
 // Epilogue: dQ = bf16(scale * accumulator), 8 lanes per (token, head) row.
 // ----------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) attn_bwd_epilogue_kernel(const BwdParams p) {
+  pdl_wait();  // the accumulator is complete when the main kernel is
+  pdl_launch_dependents();
   const int64_t n_rows = p.total_q * p.heads;
   const int lane8 = threadIdx.x & 7;
   int64_t row = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
@@ -171,14 +188,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+
+  // delta, the cleared dQ accumulator and the work list come from the prologue kernel.
+  pdl_wait();
+  pdl_launch_dependents();
 
   int q_begin = 0, k_begin = 0, lq = p.lq, lk = p.lk, bcoord = b;
   if (p.cu_q != nullptr) {
-    q_begin = p.cu_q[b];
-    lq = p.cu_q[b + 1] - q_begin;
-    k_begin = p.cu_k[b];
-    lk = p.cu_k[b + 1] - k_begin;
+    // One read tells the CTA everything about its item (the sequence index `batch` stands for the
+    // rows past the last sequence: keys without queries, which get dK = dV = 0).
+    const SchedItem item = sched_load(p.items, blockIdx.x % uint32_t(p.sched.n_items));
+    if (item.seq < 0) return;
+    h = blockIdx.x / uint32_t(p.sched.n_items);
+    b = item.seq;
+    kt = item.tile;
+    k_begin = item.own_begin;
+    lk = item.own_len;
+    q_begin = item.other_begin;
+    lq = item.other_len;
     bcoord = 0;
   }
   const int k_row0 = kt * kTile;
@@ -290,7 +318,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       // Warp 12+q owns tensor-memory lane quadrant q. It stages its 32 rows (two 32-column halves,
       // 128-byte swizzled rows) in shared memory and one lane issues the TMA add-reductions, so
       // only warp-level synchronisation is needed and L2 receives whole 128-byte lines. Rows past
-      // the end of the sequence hold exact zeros (their P^T column is 0), so adding them is harmless.
+      // the end of the sequence are staged as exact zeros, so adding them is harmless.
       setmaxnreg_dec<kBwdDrainRegs>();
       const int quad = warp & 3;
       const uint32_t lane_off = uint32_t(quad * 32) << 16;

@@ -8,10 +8,19 @@
 #include <cuda_runtime.h>
 
 #include <mutex>
+#include <utility>
+#include <vector>
 
 #include "bwd_kernel.cuh"
 #include "fwd_kernel.cuh"
+#include "sched_kernel.cuh"
 #include "selftest_kernel.cuh"
+
+// Build-time switch: 0 launches every kernel with plain stream order instead of programmatic
+// dependent launch (the kernels' griddepcontrol instructions are then no-ops).
+#ifndef NB_ATTN_PDL
+#define NB_ATTN_PDL 1
+#endif
 
 namespace {
 
@@ -78,7 +87,7 @@ int check_tensor(const nb_attn_tensor& t, bool dense) {
 int check_shape(const nb_attn_shape& s) {
   if (s.head_dim != nb::kHeadDim) return NB_ATTN_ERR_HEAD_DIM;
   if (s.batch <= 0 || s.heads <= 0 || s.max_seqlen_q <= 0 || s.max_seqlen_k <= 0) return NB_ATTN_ERR_SHAPE;
-  if (s.batch > 65535 || s.heads > 65535) return NB_ATTN_ERR_SHAPE;
+  if (s.batch > 65534 || s.heads > 65535) return NB_ATTN_ERR_SHAPE;
   if ((s.cu_seqlens_q == nullptr) != (s.cu_seqlens_k == nullptr)) return NB_ATTN_ERR_SHAPE;
   if (s.total_q <= 0 || s.total_k <= 0) return NB_ATTN_ERR_SHAPE;
   if (s.cu_seqlens_q == nullptr) {
@@ -86,6 +95,10 @@ int check_shape(const nb_attn_shape& s) {
       return NB_ATTN_ERR_SHAPE;
   } else {
     if (s.total_q > INT32_MAX || s.total_k > INT32_MAX) return NB_ATTN_ERR_SHAPE;
+    // The grid is items x heads.
+    if (nb::sched_capacity(s.total_q, s.batch) * s.heads > INT32_MAX ||
+        nb::sched_capacity(s.total_k, s.batch) * s.heads > INT32_MAX)
+      return NB_ATTN_ERR_SHAPE;
   }
   if (!(s.scale > 0.f)) return NB_ATTN_ERR_SHAPE;
   return NB_ATTN_OK;
@@ -127,11 +140,54 @@ int make_dq_accum_tmap(CUtensorMap* map, float* accum, int64_t total_q, int head
 
 constexpr float kLog2e = 1.4426950408889634f;
 
+// Launch with programmatic stream serialization: the kernel may become resident while its
+// predecessor in the stream drains; it orders itself with griddepcontrol.wait (ptx.cuh).
+template <typename... KArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = NB_ATTN_PDL ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// side 0: query tiles are the items; side 1: key tiles are.
+nb::SchedParams make_sched(const nb_attn_shape& s, int side, nb::SchedItem* items, int64_t n_items, int32_t* status) {
+  nb::SchedParams sp;
+  const bool fwd = side == 0;
+  sp.cu_own = fwd ? s.cu_seqlens_q : s.cu_seqlens_k;
+  sp.cu_other = fwd ? s.cu_seqlens_k : s.cu_seqlens_q;
+  sp.batch = s.batch;
+  sp.max_own = fwd ? s.max_seqlen_q : s.max_seqlen_k;
+  sp.max_other = fwd ? s.max_seqlen_k : s.max_seqlen_q;
+  sp.total_own = fwd ? s.total_q : s.total_k;
+  sp.total_other = fwd ? s.total_k : s.total_q;
+  sp.items = items;
+  sp.n_items = int32_t(n_items);
+  sp.status = status;
+  return sp;
+}
+
+// Layout of the backward workspace: fp32 dQ accumulator | fp32 delta | work list (varlen only).
+size_t bwd_accum_bytes(const nb_attn_shape& s) { return size_t(s.total_q) * size_t(s.heads) * nb::kHeadDim * sizeof(float); }
+size_t bwd_delta_bytes(const nb_attn_shape& s) { return size_t(s.total_q) * size_t(s.heads) * sizeof(float); }
+size_t bwd_items_offset(const nb_attn_shape& s) { return align_up(bwd_accum_bytes(s) + bwd_delta_bytes(s), 256); }
+
 int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // Scratch for nb_attn_bwd_builtin_scratch: one fixed array in the library image per GPU. The name
 // below is only a host-side handle; kernels get the device address looked up per device.
-constexpr size_t kBuiltinScratchBytes = size_t(NB_ATTN_BUILTIN_SCRATCH_ROWS) * (nb::kHeadDim * sizeof(float) + sizeof(float));
+constexpr size_t kBuiltinScratchBytes =
+    size_t(NB_ATTN_BUILTIN_SCRATCH_ROWS) * (nb::kHeadDim * sizeof(float) + sizeof(float)) + 256 +
+    size_t(NB_ATTN_BUILTIN_SCRATCH_ITEMS) * sizeof(nb::SchedItem);
 static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
 void* g_builtin_scratch_addr[kMaxDevices];  // device address of the array, per device, once looked up
 
@@ -150,20 +206,25 @@ int builtin_scratch_address(void** out) {
   return NB_ATTN_OK;
 }
 
-int launch_bwd(const nb_attn_bwd_args* a, void* workspace, size_t workspace_bytes, void* stream) {
+// Everything about a backward call that can be checked without touching CUDA.
+int validate_bwd(const nb_attn_bwd_args* a) {
   if (a == nullptr) return NB_ATTN_ERR_NULL;
   int rc = check_shape(a->shape);
   if (rc) return rc;
-  const nb_attn_shape& s = a->shape;
-  const bool dense = s.cu_seqlens_q == nullptr;
+  const bool dense = a->shape.cu_seqlens_q == nullptr;
   const nb_attn_tensor* ts[] = {&a->q, &a->k, &a->v, &a->o, &a->d_o, &a->dq, &a->dk, &a->dv};
   for (const nb_attn_tensor* t : ts)
     if ((rc = check_tensor(*t, dense))) return rc;
   if (a->lse == nullptr) return NB_ATTN_ERR_NULL;
-  const size_t need = nb_attn_bwd_workspace_bytes(s.total_q, s.heads, s.head_dim);
-  if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
-    return NB_ATTN_ERR_WORKSPACE;
-  if ((rc = ensure_device_ready())) return rc;
+  return NB_ATTN_OK;
+}
+
+// `a` has passed validate_bwd and the device is ready.
+int launch_bwd(const nb_attn_bwd_args* a, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = NB_ATTN_OK;
+  const nb_attn_shape& s = a->shape;
+  const bool dense = s.cu_seqlens_q == nullptr;
+  if (workspace_bytes < nb_attn_bwd_workspace_bytes(&s)) return NB_ATTN_ERR_WORKSPACE;
 
   CUtensorMap tq, tk, tv, tg, tdq;
   if ((rc = make_tmap(&tq, a->q, s, true)) || (rc = make_tmap(&tk, a->k, s, false)) ||
@@ -202,20 +263,38 @@ int launch_bwd(const nb_attn_bwd_args* a, void* workspace, size_t workspace_byte
   p.lq = s.max_seqlen_q;
   p.lk = s.max_seqlen_k;
   p.total_q = s.total_q;
+  p.total_k = s.total_k;
   p.scale = s.scale;
   p.scale_log2 = s.scale * kLog2e;
   p.status = a->status;
+  dim3 grid(ceil_div(s.max_seqlen_k, nb::kTile), s.heads, s.batch);
+  if (dense) {
+    p.items = nullptr;
+    p.sched = nb::SchedParams{};
+  } else {
+    // Block 0 of the prologue builds the list of key tiles; the main kernel runs items x heads CTAs.
+    const int64_t n_items = nb::sched_capacity(s.total_k, s.batch);
+    nb::SchedItem* items =
+        reinterpret_cast<nb::SchedItem*>(static_cast<unsigned char*>(workspace) + bwd_items_offset(s));
+    p.items = items;
+    p.sched = make_sched(s, 1, items, n_items, a->status);
+    grid = dim3(unsigned(n_items * s.heads), 1, 1);
+  }
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t rows = s.total_q * s.heads;
   const int64_t want_blocks = (rows * 8 + 255) / 256;
   const int aux_blocks = int(want_blocks < 148 * 16 ? want_blocks : 148 * 16);
-  nb::attn_bwd_prologue_kernel<<<aux_blocks, 256, 0, st>>>(p);
+  bool ok = launch(nb::attn_bwd_prologue_kernel, dim3(aux_blocks), dim3(256), 0, st, p) == cudaSuccess;
   if (a->event_main_begin) cudaEventRecord(static_cast<cudaEvent_t>(a->event_main_begin), st);
-  const dim3 grid(ceil_div(s.max_seqlen_k, nb::kTile), s.heads, s.batch);
-  nb::attn_bwd_kernel<<<grid, nb::kBwdThreads, nb::kBwdSmemBytes, st>>>(tq, tk, tv, tg, tdq, p);
+  ok = ok && launch(nb::attn_bwd_kernel, grid, dim3(nb::kBwdThreads), nb::kBwdSmemBytes, st, tq, tk, tv, tg, tdq, p) ==
+                 cudaSuccess;
   if (a->event_main_end) cudaEventRecord(static_cast<cudaEvent_t>(a->event_main_end), st);
-  nb::attn_bwd_epilogue_kernel<<<aux_blocks, 256, 0, st>>>(p);
+  ok = ok && launch(nb::attn_bwd_epilogue_kernel, dim3(aux_blocks), dim3(256), 0, st, p) == cudaSuccess;
+  if (!ok) {
+    cudaGetLastError();  // leave no sticky "last error" behind for the caller's own checks
+    return NB_ATTN_ERR_LAUNCH;
+  }
   return cudaGetLastError() == cudaSuccess ? NB_ATTN_OK : NB_ATTN_ERR_LAUNCH;
 }
 
@@ -242,10 +321,16 @@ const char* nb_attn_strerror(int code) {
   }
 }
 
-size_t nb_attn_bwd_workspace_bytes(int64_t total_q, int32_t heads, int32_t head_dim) {
-  if (total_q <= 0 || heads <= 0 || head_dim <= 0) return 0;
-  const size_t rows = size_t(total_q) * size_t(heads);
-  return rows * size_t(head_dim) * sizeof(float) + rows * sizeof(float);
+size_t nb_attn_bwd_workspace_bytes(const nb_attn_shape* shape) {
+  if (shape == nullptr || check_shape(*shape) != NB_ATTN_OK) return 0;
+  const nb_attn_shape& s = *shape;
+  if (s.cu_seqlens_q == nullptr) return bwd_accum_bytes(s) + bwd_delta_bytes(s);
+  return bwd_items_offset(s) + size_t(nb::sched_capacity(s.total_k, s.batch)) * sizeof(nb::SchedItem);
+}
+
+size_t nb_attn_fwd_workspace_bytes(const nb_attn_shape* shape) {
+  if (shape == nullptr || check_shape(*shape) != NB_ATTN_OK || shape->cu_seqlens_q == nullptr) return 0;
+  return size_t(nb::sched_capacity(shape->total_q, shape->batch)) * sizeof(nb::SchedItem);
 }
 
 int nb_attn_fwd(const nb_attn_fwd_args* a, void* stream) {
@@ -258,6 +343,10 @@ int nb_attn_fwd(const nb_attn_fwd_args* a, void* stream) {
       (rc = check_tensor(a->o, dense)))
     return rc;
   if (a->lse == nullptr) return NB_ATTN_ERR_NULL;
+  const size_t ws_need = nb_attn_fwd_workspace_bytes(&s);
+  if (ws_need > 0 && (a->workspace == nullptr || a->workspace_bytes < ws_need ||
+                      (reinterpret_cast<uintptr_t>(a->workspace) & 255u) != 0))
+    return NB_ATTN_ERR_WORKSPACE;
   if ((rc = ensure_device_ready())) return rc;
 
   CUtensorMap tq, tk, tv;
@@ -278,26 +367,57 @@ int nb_attn_fwd(const nb_attn_fwd_args* a, void* stream) {
   p.lq = s.max_seqlen_q;
   p.lk = s.max_seqlen_k;
   p.total_q = s.total_q;
+  p.total_k = s.total_k;
   p.scale_log2 = s.scale * kLog2e;
   p.status = a->status;
 
-  const dim3 grid(ceil_div(s.max_seqlen_q, nb::kFwdQRows), s.heads, s.batch);
-  nb::attn_fwd_kernel<<<grid, nb::kFwdThreads, nb::kFwdSmemBytes, static_cast<cudaStream_t>(stream)>>>(tq, tk, tv, p);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(ceil_div(s.max_seqlen_q, nb::kFwdQRows), s.heads, s.batch);
+  bool ok = true;
+  p.items = nullptr;
+  p.n_items = 0;
+  if (!dense) {
+    // The scheduler's list of query tiles, then one CTA per item and head.
+    const int64_t n_items = nb::sched_capacity(s.total_q, s.batch);
+    nb::SchedItem* items = static_cast<nb::SchedItem*>(a->workspace);
+    const nb::SchedParams sp = make_sched(s, 0, items, n_items, a->status);
+    ok = launch(nb::attn_sched_kernel, dim3(1), dim3(nb::kSchedThreads), 0, st, sp) == cudaSuccess;
+    p.items = items;
+    p.n_items = int32_t(n_items);
+    grid = dim3(unsigned(n_items * s.heads), 1, 1);
+  }
+  ok = ok && launch(nb::attn_fwd_kernel, grid, dim3(nb::kFwdThreads), nb::kFwdSmemBytes, st, tq, tk, tv, p) == cudaSuccess;
+  if (!ok) {
+    cudaGetLastError();
+    return NB_ATTN_ERR_LAUNCH;
+  }
   return cudaGetLastError() == cudaSuccess ? NB_ATTN_OK : NB_ATTN_ERR_LAUNCH;
 }
 
 int nb_attn_bwd(const nb_attn_bwd_args* a, void* stream) {
-  if (a == nullptr) return NB_ATTN_ERR_NULL;
+  int rc = validate_bwd(a);
+  if (rc) return rc;
+  if (a->workspace == nullptr || a->workspace_bytes < nb_attn_bwd_workspace_bytes(&a->shape) ||
+      (reinterpret_cast<uintptr_t>(a->workspace) & 255u) != 0)
+    return NB_ATTN_ERR_WORKSPACE;
+  if ((rc = ensure_device_ready())) return rc;
   return launch_bwd(a, a->workspace, a->workspace_bytes, stream);
 }
 
 int nb_attn_bwd_builtin_scratch(const nb_attn_bwd_args* a, void* stream) {
-  if (a == nullptr) return NB_ATTN_ERR_NULL;
-  int rc = check_shape(a->shape);
+  // Same argument checks, in the same order, as nb_attn_bwd; CUDA is touched only after them.
+  int rc = validate_bwd(a);
   if (rc) return rc;
-  if (a->shape.total_q * int64_t(a->shape.heads) > int64_t(NB_ATTN_BUILTIN_SCRATCH_ROWS)) return NB_ATTN_ERR_TOO_LARGE;
+  const nb_attn_shape& s = a->shape;
+  if (s.total_q * int64_t(s.heads) > int64_t(NB_ATTN_BUILTIN_SCRATCH_ROWS)) return NB_ATTN_ERR_TOO_LARGE;
+  if (s.cu_seqlens_q != nullptr && nb::sched_capacity(s.total_k, s.batch) > int64_t(NB_ATTN_BUILTIN_SCRATCH_ITEMS))
+    return NB_ATTN_ERR_TOO_LARGE;
+  if ((rc = ensure_device_ready())) return rc;
   void* scratch = nullptr;
-  if ((rc = builtin_scratch_address(&scratch))) return rc;
+  if ((rc = builtin_scratch_address(&scratch))) {
+    cudaGetLastError();
+    return rc;
+  }
   return launch_bwd(a, scratch, kBuiltinScratchBytes, stream);
 }
 
@@ -310,6 +430,76 @@ int nb_attn_selftest_mma(int mode, const void* a, const void* b, float* d, int32
   nb::mma_selftest_kernel<<<1, 128, nb::kSelftestSmemBytes, static_cast<cudaStream_t>(stream)>>>(
       mode, static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), d, status);
   return cudaGetLastError() == cudaSuccess ? NB_ATTN_OK : NB_ATTN_ERR_LAUNCH;
+}
+
+int nb_attn_selftest_wait(uint64_t limit_ns, int32_t* status, int32_t* out, void* stream) {
+  if (status == nullptr) return NB_ATTN_ERR_NULL;
+  if (limit_ns == 0 || limit_ns > 1000000000ull) return NB_ATTN_ERR_SHAPE;  // at most one second
+  int rc = ensure_device_ready();
+  if (rc) return rc;
+  nb::wait_selftest_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns, status, out);
+  return cudaGetLastError() == cudaSuccess ? NB_ATTN_OK : NB_ATTN_ERR_LAUNCH;
+}
+
+int64_t nb_attn_schedule_capacity(int64_t total_tokens, int32_t batch) {
+  if (total_tokens < 0 || batch <= 0) return 0;
+  return nb::sched_capacity(total_tokens, batch);
+}
+
+int nb_attn_schedule_build(const nb_attn_shape* shape, int side, nb_attn_sched_item* items, int64_t n_items,
+                           int32_t* status, void* stream) {
+  if (shape == nullptr || items == nullptr) return NB_ATTN_ERR_NULL;
+  int rc = check_shape(*shape);
+  if (rc) return rc;
+  if (shape->cu_seqlens_q == nullptr || (side != 0 && side != 1)) return NB_ATTN_ERR_SHAPE;
+  if (n_items < nb::sched_capacity(side == 0 ? shape->total_q : shape->total_k, shape->batch) || n_items > INT32_MAX)
+    return NB_ATTN_ERR_WORKSPACE;
+  if ((rc = ensure_device_ready())) return rc;
+  const nb::SchedParams sp = make_sched(*shape, side, reinterpret_cast<nb::SchedItem*>(items), n_items, status);
+  if (launch(nb::attn_sched_kernel, dim3(1), dim3(nb::kSchedThreads), 0, static_cast<cudaStream_t>(stream), sp) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    return NB_ATTN_ERR_LAUNCH;
+  }
+  return NB_ATTN_OK;
+}
+
+int nb_attn_schedule_host(const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k, int32_t batch,
+                          int32_t max_seqlen_q, int32_t max_seqlen_k, int64_t total_q, int64_t total_k, int side,
+                          nb_attn_sched_item* items_out, int64_t n_items) {
+  if (cu_seqlens_q == nullptr || cu_seqlens_k == nullptr || items_out == nullptr) return NB_ATTN_ERR_NULL;
+  nb::SchedItem* items = reinterpret_cast<nb::SchedItem*>(items_out);
+  if (batch <= 0 || batch > 65534 || (side != 0 && side != 1) || n_items > INT32_MAX) return NB_ATTN_ERR_SHAPE;
+  nb_attn_shape s = {};
+  s.batch = batch;
+  s.max_seqlen_q = max_seqlen_q;
+  s.max_seqlen_k = max_seqlen_k;
+  s.total_q = total_q;
+  s.total_k = total_k;
+  s.cu_seqlens_q = cu_seqlens_q;
+  s.cu_seqlens_k = cu_seqlens_k;
+  const nb::SchedParams sp = make_sched(s, side, items, n_items, nullptr);
+  if (n_items < nb::sched_capacity(sp.total_own, batch)) return NB_ATTN_ERR_WORKSPACE;
+  // Same classification as the device kernel; buckets in order, sequences ascending inside one.
+  std::vector<std::vector<int>> by_bucket(nb::kSchedBuckets);
+  for (int i = 0; i <= batch; ++i) {  // i == batch: the rows past the last sequence
+    const nb::SchedSeq q = nb::sched_classify(sp, i);
+    if (!q.ok) return NB_ATTN_ERR_SHAPE;
+    by_bucket[q.bucket].push_back(i);
+  }
+  int64_t at = 0;
+  for (const auto& seqs : by_bucket)
+    for (int i : seqs) {
+      const nb::SchedSeq q = nb::sched_classify(sp, i);
+      for (int t = 0; t < q.full; ++t) items[at++] = nb::sched_item(q, i, t);
+    }
+  for (const auto& seqs : by_bucket)
+    for (int i : seqs) {
+      const nb::SchedSeq q = nb::sched_classify(sp, i);
+      if (q.ragged) items[at++] = nb::sched_item(q, i, q.full);
+    }
+  for (; at < n_items; ++at) items[at] = nb::sched_no_item();
+  return NB_ATTN_OK;
 }
 
 }  // extern "C"

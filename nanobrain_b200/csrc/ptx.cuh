@@ -49,6 +49,18 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-stream-serialization
+// attribute may start while its predecessor in the stream is still running. pdl_wait() blocks until
+// the predecessor has completed and its writes are visible; pdl_launch_dependents() lets the
+// successor's CTAs be scheduled as soon as every CTA of this grid has called it or exited. Each
+// kernel here calls pdl_launch_dependents() only after its own pdl_wait(), so when a CTA of kernel N
+// runs, everything before kernel N-1 in the stream is complete: before its wait a kernel may read
+// whatever kernel N-1 does not write.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ----------------------------------------------------------------------------------------
 // mbarrier
 // ----------------------------------------------------------------------------------------
@@ -79,14 +91,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Status codes written to the caller's status word when a bounded wait gives up.
-enum : int { kStatusOk = 0, kStatusWaitTimeout = 1 };
+// Status codes written to the caller's status word: a bounded wait gave up, or the work-list
+// builder found cu_seqlens that are not a valid packing (see sched_kernel.cuh).
+enum : int { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadSeqlens = 2 };
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // about two seconds
 
-// Bounded wait. `abort_flag` lives in shared memory and is shared by the whole CTA.
+// Bounded wait. `abort_flag` lives in shared memory and is shared by the whole CTA. The attention
+// kernels use the default limit (a compile-time constant); the wait self-test passes its own.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status_word) {
+                                          int* status_word, uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
@@ -96,7 +110,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         if (status_word) atomicExch(status_word, (int)kStatusWaitTimeout);
         return false;
@@ -278,6 +292,10 @@ __device__ __forceinline__ void mbar_wait2(uint32_t bar_a, uint32_t par_a, uint3
 __host__ __device__ constexpr uint32_t make_idesc(int m, int n, int a_mn_major, int b_mn_major) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (uint32_t(a_mn_major) << 15) |
          (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) | (uint32_t(m >> 4) << 24);
+}
+// The same descriptor with another N (a multiple of 16 for M = 128), for MMAs over a ragged tile.
+__host__ __device__ constexpr uint32_t idesc_with_n(uint32_t idesc, int n) {
+  return (idesc & ~(0x3Fu << 17)) | (uint32_t(n >> 3) << 17);
 }
 
 // Shared-memory matrix descriptor for the 128-byte-swizzled layouts used here. Every operand

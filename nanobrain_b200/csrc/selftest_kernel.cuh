@@ -106,4 +106,46 @@ mma_selftest_kernel(int mode, const __nv_bfloat16* __restrict__ A, const __nv_bf
   }
 }
 
+// Self-test of the bounded wait: one CTA allocates tensor memory, then all its warps wait on an
+// mbarrier that nothing will ever arrive on, with the caller's limit instead of the kernels' two
+// seconds. The wait gives up, the status word receives kStatusWaitTimeout, the tensor memory is
+// freed and the kernel returns -- what every attention kernel does if one of its waits runs out.
+// out[0] = 1 if the first wait returned "gave up", out[1] = 1 if a later wait returned at once
+// because of the CTA-wide abort flag.
+__global__ void __launch_bounds__(128) wait_selftest_kernel(uint64_t limit_ns, int32_t* status, int32_t* out) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(smem_u32(&tmem_base_slot), 512);  // everything: a leak would block the next kernel
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const bool first = mbar_wait(smem_u32(&bar), 0, &abort_flag, status, limit_ns);
+  __syncthreads();
+  const uint64_t t0 = globaltimer_ns();
+  const bool second = mbar_wait(smem_u32(&bar), 0, &abort_flag, status, limit_ns);
+  const uint64_t waited = globaltimer_ns() - t0;
+  if (tid == 0 && out != nullptr) {
+    out[0] = first ? 0 : 1;
+    out[1] = (!second && waited < limit_ns) ? 1 : 0;
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base_slot, 512);
+  }
+}
+
 }  // namespace nb

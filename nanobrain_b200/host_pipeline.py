@@ -78,7 +78,8 @@ class HostPipeline:
         with torch.cuda.device(self.device):
             self.dev_in = [torch.empty(shape, dtype=torch.bfloat16, device=self.device) for _ in range(4)]
             self.dev_out = [torch.empty(shape, dtype=torch.bfloat16, device=self.device) for _ in range(4)]
-            self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+            # Pinned host memory the kernels can write to: readable at any time without a sync.
+            self.status = torch.zeros(1, dtype=torch.int32).pin_memory()
             self.s_in, self.s_compute, self.s_out = (torch.cuda.Stream(self.device) for _ in range(3))
         self.groups = []
         for run in split_sequences(self.lengths, groups):
@@ -88,20 +89,22 @@ class HostPipeline:
                 continue
             lens = self.lengths[run.start:run.stop]
             cu = torch.tensor([s - t0 for s in starts[run.start:run.stop + 1]], dtype=torch.int32, device=self.device)
-            ws_bytes = self.lib.nb_attn_bwd_workspace_bytes(tokens, self.heads, HEAD_DIM)
+            sh = _lib.Shape(len(lens), self.heads, HEAD_DIM, max(lens), max(lens), tokens, tokens,
+                            cu.data_ptr(), cu.data_ptr(), self.scale)
+            ws_bytes, fws_bytes = _lib.bwd_workspace_bytes(sh), _lib.fwd_workspace_bytes(sh)
             with torch.cuda.device(self.device):
                 lse = torch.empty((self.heads, tokens), dtype=torch.float32, device=self.device)
                 ws = torch.empty(ws_bytes, dtype=torch.uint8, device=self.device)
+                fws = torch.empty(fws_bytes, dtype=torch.uint8, device=self.device)
             sl = slice(t0, t1)
             q, k, v, g = (t[sl] for t in self.dev_in)
             o, dq, dk, dv = (t[sl] for t in self.dev_out)
-            sh = _lib.Shape(len(lens), self.heads, HEAD_DIM, max(lens), max(lens), tokens, tokens,
-                            cu.data_ptr(), cu.data_ptr(), self.scale)
             d = self._desc
-            fwd = _lib.FwdArgs(sh, d(q), d(k), d(v), d(o), lse.data_ptr(), self.status.data_ptr())
+            fwd = _lib.FwdArgs(sh, d(q), d(k), d(v), d(o), lse.data_ptr(), self.status.data_ptr(),
+                               fws.data_ptr(), fws_bytes)
             bwd = _lib.BwdArgs(sh, d(q), d(k), d(v), d(o), d(g), d(dq), d(dk), d(dv), lse.data_ptr(),
                                ws.data_ptr(), ws_bytes, self.status.data_ptr(), None, None)
-            self.groups.append({"slice": sl, "fwd": fwd, "bwd": bwd, "keep": (cu, lse, ws),
+            self.groups.append({"slice": sl, "fwd": fwd, "bwd": bwd, "keep": (cu, lse, ws, fws),
                                 "ev_in": torch.cuda.Event(), "ev_done": torch.cuda.Event(),
                                 "ev_out": torch.cuda.Event()})
 
@@ -161,6 +164,8 @@ class HostPipeline:
         """Synchronise and raise if a kernel reported a timed-out wait."""
         self.wait()
         torch.cuda.synchronize(self.device)
-        code = int(self.status.item())
+        code = int(self.status[0])
         if code != 0:
-            raise RuntimeError(f"attention kernel reported device status {code}")
+            self.status.zero_()
+            raise RuntimeError(f"attention kernel reported device status {code}: "
+                               f"{_lib.STATUS_TEXT.get(code, 'unknown code')}")

@@ -38,23 +38,39 @@ _status_words: dict[int, Tensor] = {}
 
 
 def _status_word(device: torch.device) -> Tensor:
-    """One int32 per device that kernels write to if a bounded wait gives up."""
+    """One int32 per device that kernels write to when something went wrong on the device.
+
+    The word lives in pinned host memory, which the GPU addresses directly: a kernel's rare write
+    goes over the bus, and the host can look at the word at any time without synchronising."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
     t = _status_words.get(idx)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        t = torch.zeros(1, dtype=torch.int32).pin_memory()
         _status_words[idx] = t
     return t
 
 
-def check_status(device: Optional[torch.device] = None) -> None:
-    """Synchronise and raise if any kernel launched so far on ``device`` reported a problem."""
-    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    word = _status_word(device)
-    code = int(word.item())
+def _raise_for_status(word: Tensor) -> None:
+    code = int(word[0])
     if code != 0:
         word.zero_()
-        raise RuntimeError(f"nanobrain_b200 attention kernel reported device status {code} (1 = a bounded wait timed out)")
+        text = _lib.STATUS_TEXT.get(code, "unknown code")
+        raise RuntimeError(f"nanobrain_b200 attention kernel reported device status {code}: {text}")
+
+
+def poll_status(device: Optional[torch.device] = None) -> None:
+    """Raise if a kernel that has already finished reported a problem. Never synchronises: every
+    op calls this before it launches, so a failed step surfaces at the next attention call."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    _raise_for_status(_status_word(device))
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Synchronise with ``device`` and raise if any kernel launched so far reported a problem.
+    Call it where the training step synchronises anyway (for example where the loss is read)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    torch.cuda.synchronize(device)
+    _raise_for_status(_status_word(device))
 
 
 def _require(cond: bool, msg: str) -> None:
@@ -116,6 +132,10 @@ def _stream_ptr() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+def _before_launch(device: torch.device) -> None:
+    poll_status(device)
+
+
 def _after_launch(device: torch.device) -> None:
     if _DEBUG:
         check_status(device)
@@ -135,11 +155,12 @@ def sdpa_fwd(q: Tensor, k: Tensor, v: Tensor, scale: float) -> tuple[Tensor, Ten
     out = _new_dense(q)
     lse = torch.empty((b, h, lq), dtype=torch.float32, device=q.device)
     lib = _lib.load()
+    _before_launch(q.device)
     with torch.cuda.device(q.device):
         args = _lib.FwdArgs(
             _lib.Shape(b, h, d, lq, lk, b * lq, b * lk, None, None, scale),
             _dense_desc(q), _dense_desc(k), _dense_desc(v), _dense_desc(out),
-            lse.data_ptr(), _status_word(q.device).data_ptr(),
+            lse.data_ptr(), _status_word(q.device).data_ptr(), None, 0,
         )
         _lib.check(lib.nb_attn_fwd(C.byref(args), _stream_ptr()), "nb_attn_fwd")
     _after_launch(q.device)
@@ -165,11 +186,13 @@ def sdpa_bwd(
     lse = lse.contiguous()
     dq, dk, dv = _new_dense(q), _new_dense(k), _new_dense(v)
     lib = _lib.load()
-    ws_bytes = lib.nb_attn_bwd_workspace_bytes(b * lq, h, d)
+    _before_launch(q.device)
+    shape = _lib.Shape(b, h, d, lq, lk, b * lq, b * lk, None, None, scale)
+    ws_bytes = _lib.bwd_workspace_bytes(shape)
     workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
         args = _lib.BwdArgs(
-            _lib.Shape(b, h, d, lq, lk, b * lq, b * lk, None, None, scale),
+            shape,
             _dense_desc(q), _dense_desc(k), _dense_desc(v), _dense_desc(out), _dense_desc(d_out),
             _dense_desc(dq), _dense_desc(dk), _dense_desc(dv),
             lse.data_ptr(), workspace.data_ptr(), ws_bytes, _status_word(q.device).data_ptr(),
@@ -227,12 +250,15 @@ def sdpa_varlen_fwd(
     out = torch.empty((tq, h, d), dtype=q.dtype, device=q.device)
     lse = torch.empty((h, tq), dtype=torch.float32, device=q.device)
     lib = _lib.load()
+    _before_launch(q.device)
+    shape = _lib.Shape(nseq, h, d, max_seqlen_q, max_seqlen_k, tq, tk,
+                       cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), scale)
+    ws_bytes = _lib.fwd_workspace_bytes(shape)  # the scheduler's work list
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
         args = _lib.FwdArgs(
-            _lib.Shape(nseq, h, d, max_seqlen_q, max_seqlen_k, tq, tk,
-                       cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), scale),
-            _packed_desc(q), _packed_desc(k), _packed_desc(v), _packed_desc(out),
-            lse.data_ptr(), _status_word(q.device).data_ptr(),
+            shape, _packed_desc(q), _packed_desc(k), _packed_desc(v), _packed_desc(out),
+            lse.data_ptr(), _status_word(q.device).data_ptr(), workspace.data_ptr(), ws_bytes,
         )
         _lib.check(lib.nb_attn_fwd(C.byref(args), _stream_ptr()), "nb_attn_fwd")
     _after_launch(q.device)
@@ -262,12 +288,14 @@ def sdpa_varlen_bwd(
     dk = torch.empty((tk, h, d), dtype=q.dtype, device=q.device)
     dv = torch.empty((tk, h, d), dtype=q.dtype, device=q.device)
     lib = _lib.load()
-    ws_bytes = lib.nb_attn_bwd_workspace_bytes(tq, h, d)
+    _before_launch(q.device)
+    shape = _lib.Shape(nseq, h, d, max_seqlen_q, max_seqlen_k, tq, tk,
+                       cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), scale)
+    ws_bytes = _lib.bwd_workspace_bytes(shape)
     workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
         args = _lib.BwdArgs(
-            _lib.Shape(nseq, h, d, max_seqlen_q, max_seqlen_k, tq, tk,
-                       cu_seqlens_q.data_ptr(), cu_seqlens_k.data_ptr(), scale),
+            shape,
             _packed_desc(q), _packed_desc(k), _packed_desc(v), _packed_desc(out), _packed_desc(d_out),
             _packed_desc(dq), _packed_desc(dk), _packed_desc(dv),
             lse.data_ptr(), workspace.data_ptr(), ws_bytes, _status_word(q.device).data_ptr(),

@@ -42,9 +42,19 @@ def test_abi_version_and_strerror(lib):
 
 
 def test_workspace_bytes(lib):
-    # fp32 dQ accumulator [T][H][64] + fp32 delta [H*T]
-    assert lib.nb_attn_bwd_workspace_bytes(26253, 12, 64) == 26253 * 12 * (64 * 4 + 4)
-    assert lib.nb_attn_bwd_workspace_bytes(0, 12, 64) == 0
+    # dense: fp32 dQ accumulator [T][H][64] + fp32 delta [H*T]; the forward needs nothing
+    dense = _shape(batch=2, heads=12, max_seqlen_q=820, max_seqlen_k=820, total_q=1640, total_k=1640)
+    assert _lib.bwd_workspace_bytes(dense) == 1640 * 12 * (64 * 4 + 4)
+    assert _lib.fwd_workspace_bytes(dense) == 0
+    # varlen: plus the work list, total / 128 + batch + 1 entries of 32 bytes (after 256-byte alignment)
+    packed = _shape(batch=32, heads=12, max_seqlen_q=920, max_seqlen_k=920, total_q=26253, total_k=26253,
+                    cu_seqlens_q=0x100, cu_seqlens_k=0x100)
+    items = 26253 // 128 + 32 + 1
+    assert lib.nb_attn_schedule_capacity(26253, 32) == items
+    assert _lib.fwd_workspace_bytes(packed) == 32 * items
+    accum = 26253 * 12 * (64 * 4 + 4)
+    assert _lib.bwd_workspace_bytes(packed) == (accum + 255) // 256 * 256 + 32 * items
+    assert _lib.bwd_workspace_bytes(_shape(batch=0)) == 0
 
 
 def _shape(**kw):
@@ -61,24 +71,28 @@ def _tensor(ptr=0x10000, sb=2048, st=128, sh=64):
 def test_fwd_rejects_bad_arguments_without_a_gpu(lib):
     ok = _tensor()
     cases = [
-        (_lib.FwdArgs(_shape(head_dim=128), ok, ok, ok, ok, 0x10000, None), 2),
-        (_lib.FwdArgs(_shape(batch=0), ok, ok, ok, ok, 0x10000, None), 3),
-        (_lib.FwdArgs(_shape(total_q=17), ok, ok, ok, ok, 0x10000, None), 3),
-        (_lib.FwdArgs(_shape(scale=0.0), ok, ok, ok, ok, 0x10000, None), 3),
-        (_lib.FwdArgs(_shape(cu_seqlens_q=0x100), ok, ok, ok, ok, 0x10000, None), 3),
-        (_lib.FwdArgs(_shape(), _tensor(ptr=None), ok, ok, ok, 0x10000, None), 1),
-        (_lib.FwdArgs(_shape(), _tensor(ptr=0x10008), ok, ok, ok, 0x10000, None), 4),
-        (_lib.FwdArgs(_shape(), ok, _tensor(st=100), ok, ok, 0x10000, None), 4),
-        (_lib.FwdArgs(_shape(), ok, ok, ok, ok, None, None), 1),
+        (_lib.FwdArgs(_shape(head_dim=128), ok, ok, ok, ok, 0x10000, None, None, 0), 2),
+        (_lib.FwdArgs(_shape(batch=0), ok, ok, ok, ok, 0x10000, None, None, 0), 3),
+        (_lib.FwdArgs(_shape(total_q=17), ok, ok, ok, ok, 0x10000, None, None, 0), 3),
+        (_lib.FwdArgs(_shape(scale=0.0), ok, ok, ok, ok, 0x10000, None, None, 0), 3),
+        (_lib.FwdArgs(_shape(cu_seqlens_q=0x100), ok, ok, ok, ok, 0x10000, None, None, 0), 3),
+        (_lib.FwdArgs(_shape(), _tensor(ptr=None), ok, ok, ok, 0x10000, None, None, 0), 1),
+        (_lib.FwdArgs(_shape(), _tensor(ptr=0x10008), ok, ok, ok, 0x10000, None, None, 0), 4),
+        (_lib.FwdArgs(_shape(), ok, _tensor(st=100), ok, ok, 0x10000, None, None, 0), 4),
+        (_lib.FwdArgs(_shape(), ok, ok, ok, ok, None, None, None, 0), 1),
     ]
     for args, want in cases:
         assert lib.nb_attn_fwd(C.byref(args), None) == want
     assert lib.nb_attn_fwd(None, None) == 1
+    # varlen mode needs the work-list workspace
+    packed = _shape(cu_seqlens_q=0x100, cu_seqlens_k=0x100)
+    assert lib.nb_attn_fwd(C.byref(_lib.FwdArgs(packed, ok, ok, ok, ok, 0x10000, None, None, 0)), None) == 5
+    assert lib.nb_attn_fwd(C.byref(_lib.FwdArgs(packed, ok, ok, ok, ok, 0x10000, None, 0x20000, 3)), None) == 5
 
 
 def test_bwd_rejects_bad_workspace_without_a_gpu(lib):
     ok = _tensor()
-    need = lib.nb_attn_bwd_workspace_bytes(16, 2, 64)
+    need = _lib.bwd_workspace_bytes(_shape())
     mk = lambda ws, nbytes: _lib.BwdArgs(_shape(), ok, ok, ok, ok, ok, ok, ok, ok, 0x10000, ws, nbytes, None, None, None)
     assert lib.nb_attn_bwd(C.byref(mk(None, need)), None) == 5
     assert lib.nb_attn_bwd(C.byref(mk(0x20000, need - 1)), None) == 5

@@ -6,8 +6,8 @@ latency-critical loop where a `cudaMalloc` would stall the device. They pass inp
 usual; the scratch the backward needs (fp32 dQ accumulator + row dots) lives in a fixed array
 inside the library instead of in `args.workspace`.
 
-The file name sorts last on purpose: these tests run after every other test, and they must also
-pass when run alone in a fresh process (the first call on a device resolves the array's address).
+The first call on a device resolves the array's address, so the GPU test passes in a fresh
+process as well as after other tests have used the library.
 """
 
 import ctypes as C
@@ -29,6 +29,30 @@ def test_problems_beyond_the_builtin_scratch_are_refused_without_a_gpu():
     assert lib.nb_attn_bwd_builtin_scratch(C.byref(args), None) == 9
     assert b"NB_ATTN_BUILTIN_SCRATCH_ROWS" in lib.nb_attn_strerror(9)
     assert lib.nb_attn_bwd_builtin_scratch(None, None) == 1
+    # a packed batch with more work-list entries than the array has room for
+    many = _lib.BUILTIN_SCRATCH_ITEMS + 1
+    too_many = _lib.Shape(many, 1, 64, 1, 1, many, many, 0x10000, 0x10000, 0.125)
+    args = _lib.BwdArgs(too_many, ok, ok, ok, ok, ok, ok, ok, ok, 0x10000, None, 0, None, None, None)
+    assert lib.nb_attn_bwd_builtin_scratch(C.byref(args), None) == 9
+
+
+def test_builtin_scratch_entry_validates_like_the_workspace_entry_without_a_gpu():
+    # Bad tensors are refused with the same codes as nb_attn_bwd, before CUDA is touched.
+    build.build()
+    lib = _lib.load()
+    ok = _lib.Tensor(0x10000, 2048, 128, 64)
+    shape = _lib.Shape(1, 2, 64, 16, 16, 16, 16, None, None, 0.125)
+    cases = [(_lib.Tensor(None, 2048, 128, 64), 1), (_lib.Tensor(0x10008, 2048, 128, 64), 4),
+             (_lib.Tensor(0x10000, 2048, 100, 64), 4)]
+    for bad, want in cases:
+        for slot in range(8):
+            tensors = [ok] * 8
+            tensors[slot] = bad
+            args = _lib.BwdArgs(shape, *tensors, 0x10000, 0x20000, 1 << 20, None, None, None)
+            assert lib.nb_attn_bwd_builtin_scratch(C.byref(args), None) == want
+            assert lib.nb_attn_bwd(C.byref(args), None) == want
+    args = _lib.BwdArgs(shape, *([ok] * 8), None, 0x20000, 1 << 20, None, None, None)  # lse missing
+    assert lib.nb_attn_bwd_builtin_scratch(C.byref(args), None) == 1
 
 
 def _backward_both_ways(lengths, heads, seed):
@@ -45,7 +69,10 @@ def _backward_both_ways(lengths, heads, seed):
     desc = lambda t: _lib.Tensor(t.data_ptr(), 0, t.stride(0), t.stride(1))
     shape = _lib.Shape(nseq, heads, 64, max_len, max_len, total, total, cu.data_ptr(), cu.data_ptr(), 0.125)
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-    fwd = _lib.FwdArgs(shape, desc(q), desc(k), desc(v), desc(out), lse.data_ptr(), status.data_ptr())
+    fws_bytes = _lib.fwd_workspace_bytes(shape)
+    fws = torch.empty(fws_bytes, dtype=torch.uint8, device=dev)
+    fwd = _lib.FwdArgs(shape, desc(q), desc(k), desc(v), desc(out), lse.data_ptr(), status.data_ptr(),
+                       fws.data_ptr(), fws_bytes)
     _lib.check(lib.nb_attn_fwd(C.byref(fwd), stream), "nb_attn_fwd")
 
     results = []
@@ -54,7 +81,7 @@ def _backward_both_ways(lengths, heads, seed):
         if builtin:
             ws, ws_ptr, ws_bytes = None, None, 0  # no workspace is passed at all
         else:
-            ws_bytes = lib.nb_attn_bwd_workspace_bytes(total, heads, 64)
+            ws_bytes = _lib.bwd_workspace_bytes(shape)
             ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
             ws_ptr = ws.data_ptr()
         args = _lib.BwdArgs(shape, desc(q), desc(k), desc(v), desc(out), desc(g), desc(dq), desc(dk), desc(dv),
