@@ -26,7 +26,7 @@
 //   attn_bwd_epilogue_kernel : dQ = bf16(scale * accumulator). HBM-bound.
 //
 // Packed mode: block 0 of the prologue also builds the scheduler's work list of key tiles
-// (sched_kernel.cuh) and the main kernel's grid runs the whole list once per head. A ragged tile is computed at full
+// (sched_kernel.cuh) and the main kernel's grid is items x heads (the heads of one item adjacent). A ragged tile is computed at full
 // width and masked: rows of the NEXT packed sequence that it brings into shared memory are
 // multiplied by exact zeros of P^T / dS^T. For finite data that is exact; if the next sequence's
 // first rows hold Inf or NaN, 0 x Inf makes this sequence's gradients NaN as well (the forward
@@ -50,7 +50,7 @@ struct BwdParams {
   float* dq_accum;  // fp32 [total_q][heads][64]
   const int32_t* cu_q;
   const int32_t* cu_k;
-  const SchedItem* items;  // packed mode: work list of key tiles; CTA x runs entry x % n_items for head x / n_items
+  const SchedItem* items;  // packed mode: work list of key tiles; CTA x runs entry x / heads for head x % heads
   SchedParams sched;      // packed mode: what block 0 of the prologue builds (items == NULL: nothing)
   int32_t batch, heads;
   int32_t lq, lk;
@@ -198,9 +198,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   if (p.cu_q != nullptr) {
     // One read tells the CTA everything about its item (the sequence index `batch` stands for the
     // rows past the last sequence: keys without queries, which get dK = dV = 0).
-    const SchedItem item = sched_load(p.items, blockIdx.x % uint32_t(p.sched.n_items));
+    const SchedItem item = sched_load(p.items, blockIdx.x / uint32_t(p.heads));
     if (item.seq < 0) return;
-    h = blockIdx.x / uint32_t(p.sched.n_items);
+    h = blockIdx.x % uint32_t(p.heads);
     b = item.seq;
     kt = item.tile;
     k_begin = item.own_begin;

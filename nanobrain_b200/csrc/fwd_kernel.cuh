@@ -3,9 +3,9 @@
 //
 // One CTA owns one 128-row query tile of one (sequence, head) and walks the sequence's keys in
 // 128-row tiles. In packed mode the CTA takes its (sequence, tile) from the scheduler's work list
-// (sched_kernel.cuh: most expensive items first; the grid runs the whole list once per head, so the
-// query tiles of one (sequence, head), which share their K/V tiles through L2, are neighbours in
-// launch order and the cheap ragged tiles of the last head fill the final wave); in dense mode the grid is
+// (sched_kernel.cuh: grid = items x heads with the heads of one item adjacent, so that launch order
+// is most expensive first over the whole grid; running the list once per head instead was measured
+// slower on mixes of short and long sequences); in dense mode the grid is
 // (tiles, heads, batch). Two CTAs are resident per SM (256 tensor-memory columns and 80 KB of shared
 // memory each), so one CTA's softmax, prologue and epilogue overlap the other's MMAs. A ragged last
 // key tile is trimmed: its score MMA runs with N rounded up to 16, the P V MMA with as many K steps,
@@ -41,8 +41,7 @@ struct FwdParams {
   float* lse;
   const int32_t* cu_q;  // NULL => dense
   const int32_t* cu_k;
-  const SchedItem* items;  // packed mode: the scheduler's work list; CTA x runs entry x % n_items for head x / n_items
-  int32_t n_items;
+  const SchedItem* items;  // packed mode: the scheduler's work list; CTA x runs entry x / heads for head x % heads
   int32_t batch, heads;
   int32_t lq, lk;  // dense lengths (max_seqlen in varlen mode)
   int64_t total_q, total_k;
@@ -127,9 +126,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   if (p.cu_q != nullptr) {
     // One read tells the CTA everything about its item (the sequence index `batch` stands for the
     // rows past the last sequence: queries without keys, which get O = 0 and LSE = -inf).
-    const SchedItem item = sched_load(p.items, blockIdx.x % uint32_t(p.n_items));
+    const SchedItem item = sched_load(p.items, blockIdx.x / uint32_t(p.heads));
     if (item.seq < 0) return;
-    h = blockIdx.x / uint32_t(p.n_items);
+    h = blockIdx.x % uint32_t(p.heads);
     b = item.seq;
     qt = item.tile;
     q_begin = item.own_begin;

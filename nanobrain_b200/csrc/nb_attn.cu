@@ -375,7 +375,6 @@ int nb_attn_fwd(const nb_attn_fwd_args* a, void* stream) {
   dim3 grid(ceil_div(s.max_seqlen_q, nb::kFwdQRows), s.heads, s.batch);
   bool ok = true;
   p.items = nullptr;
-  p.n_items = 0;
   if (!dense) {
     // The scheduler's list of query tiles, then one CTA per item and head.
     const int64_t n_items = nb::sched_capacity(s.total_q, s.batch);
@@ -383,7 +382,6 @@ int nb_attn_fwd(const nb_attn_fwd_args* a, void* stream) {
     const nb::SchedParams sp = make_sched(s, 0, items, n_items, a->status);
     ok = launch(nb::attn_sched_kernel, dim3(1), dim3(nb::kSchedThreads), 0, st, sp) == cudaSuccess;
     p.items = items;
-    p.n_items = int32_t(n_items);
     grid = dim3(unsigned(n_items * s.heads), 1, 1);
   }
   ok = ok && launch(nb::attn_fwd_kernel, grid, dim3(nb::kFwdThreads), nb::kFwdSmemBytes, st, tq, tk, tv, p) == cudaSuccess;
