@@ -41,7 +41,7 @@ NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_bwd_kernel launch, from an ncu capture of
 # this workload (only known for that workload; not measured by the run itself).
-NCU_DRAM_BYTES_BWD_MAIN = {"vitb_encoder_varlen": 364.6e6}
+NCU_DRAM_BYTES_BWD_MAIN = {"vitb_encoder_varlen": 606.9e6}
 
 
 def parse_args():
@@ -59,6 +59,7 @@ def parse_args():
     ap.add_argument("--skip-comparators", action="store_true", help="do not time torch SDPA / flash_attn beside ours")
     ap.add_argument("--skip-other-workloads", action="store_true", help="time the headline workload only")
     ap.add_argument("--skip-e2e", action="store_true", help="no host-buffer pass (for profiler captures)")
+    ap.add_argument("--skip-eval", action="store_true", help="do not time the batched varlen eval of the model mirror")
     return ap.parse_args()
 
 
@@ -448,6 +449,57 @@ def gpu_comparators(prob_varlen, prob_dense, steps: int):
     return out
 
 
+def batched_eval_images_per_s(dev, repeats: int = 3):
+    """Embeddings of ragged images with the ViT-B encoder mirror (random weights): all images packed
+    into one varlen pass (`ViTMAE3D.embed_packed`) against one encoder forward per image, the way the
+    reference's `forward_embeddings` does it (src/nanobrain/model.py:254-276). In-mask patch counts as
+    different as real brain masks are; 128^3 volumes, 8^3 patches (4096-patch grid)."""
+    import torch
+
+    from nanobrain_b200 import model as M
+
+    counts = [3200, 2900, 3475, 1, 3050, 2600, 3300, 2750]
+    torch.manual_seed(0)
+    model = M.ViTMAE3D(grid_size=(128, 128, 128), patch_size=8).to(dev).eval()
+    samples = []
+    for i, n in enumerate(counts):
+        g = torch.Generator(device=dev).manual_seed(i)
+        patches = torch.randn(4096, 512, generator=g, device=dev)
+        in_mask = torch.zeros(4096, dtype=torch.bool, device=dev)
+        in_mask[torch.randperm(4096, generator=g, device=dev)[:n]] = True
+        samples.append((patches, in_mask))
+
+    def packed():
+        return model.embed_packed(samples)
+
+    def per_image():
+        outs = []
+        with torch.inference_mode(), torch.autocast("cuda", dtype=torch.bfloat16):
+            for patches, in_mask in samples:
+                tokens = model.forward_encoder(patches[None, in_mask], model.coord_grid[:, in_mask])
+                outs.append(tokens[0, model.class_tokens:].float().mean(dim=0))
+        return outs
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(repeats):
+            out = fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / repeats, out
+
+    t_packed, a = timed(packed)
+    t_loop, b = timed(per_image)
+    worst = max(float((x["global_embedding"] - y).abs().max() / y.abs().max().clamp_min(1e-6)) for x, y in zip(a, b))
+    return {
+        "images": len(counts), "in_mask_patches": counts, "model": "ViT-B encoder mirror, depth 12, 768 wide, random weights",
+        "packed_images_per_s": len(counts) / t_packed, "per_image_loop_images_per_s": len(counts) / t_loop,
+        "max_rel_diff_of_embeddings": worst,
+        "note": "wall clock of the whole encoder (Linears, LayerNorms, attention); the per-image loop uses the same dense operator",
+    }
+
+
 def copy_only_ms(host, host_out, dev, steps: int):
     """The host-buffer path's ceiling: the same pinned H2D + D2H traffic with no kernels at all, the
     two directions on their own streams."""
@@ -635,6 +687,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 del oprob
                 torch.cuda.empty_cache()
             line["other_workloads"] = other
+        if world == 1 and not args.skip_eval and not args.skip_other_workloads:
+            line["batched_eval"] = batched_eval_images_per_s(dev)
         if world == 1:
             if not args.skip_cpu_baseline:
                 torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
