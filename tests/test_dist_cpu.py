@@ -79,3 +79,22 @@ def test_single_rank_needs_no_process_group():
     agg = bench.aggregate(bench.gather_over_ranks(stats, 1), steps=4)
     assert agg["max_ms"] == 2.0 and agg["tokens_all"] == 100
     assert abs(agg["value_tflops"] - 4e9 * 4 / 2e-3 / 1e12) < 1e-9
+
+
+def test_both_bench_arms_describe_the_same_config():
+    # the driver compares the `config` objects of the two arms; both come from shapes alone
+    import argparse
+
+    import bench
+    from nanobrain_b200 import workloads as W
+
+    for gpus in (1, 2, 8):
+        args = argparse.Namespace(workload="vitb_encoder_varlen", global_batch=0, gpus=gpus)
+        cfg = bench.workload_config(args, W.WORKLOADS[args.workload], gpus)
+        assert cfg["global_batch"] == 32 * gpus and cfg["sequences_per_gpu"] == 32
+        lengths = [W.draw_lengths(W.WORKLOADS[args.workload], seed=r) for r in range(gpus)]
+        assert cfg["tokens_all_ranks"] == sum(int(l.sum()) for l in lengths)
+        assert cfg["flops_per_step_all_ranks"] == float(sum(W.attention_flops(l, l, 12) for l in lengths))
+    strong = argparse.Namespace(workload="vitb_encoder_varlen", global_batch=256, gpus=8)
+    cfg = bench.workload_config(strong, W.WORKLOADS["vitb_encoder_varlen"], 8)
+    assert cfg["sequences_per_gpu"] == 32 and cfg["global_batch"] == 256
