@@ -437,3 +437,45 @@ def test_large_varlen_config_full_size_by_properties():
         col_sums = v1.grad[a:b].float().sum(0)               # [H, 64]: sum over keys of sum_q P[q, k] = number of queries
         assert (col_sums / (b - a) - 1).abs().max() <= 2e-2
     assert q1.grad.float().abs().max() <= 1e-2 and k1.grad.float().abs().max() <= 1e-2
+
+
+def test_scaling_config_global_batch_256_by_properties_and_shards():
+    # BASELINE config 4: the config-1 shapes with a global batch of 256 volumes, sharded B/N per GPU.
+    # One GPU's view at N = 1 (all 256 sequences) and at N = 8 (32 of them) must agree bit for bit on
+    # the forward and on dK / dV for the shared sequences (no sequence ever sees another one), the
+    # first and last sequence match fp32 MATH SDPA, and softmax rows sum to one everywhere.
+    import dataclasses
+
+    w = dataclasses.replace(W.WORKLOADS["vitb_encoder_varlen"], batch=256)
+    lengths = W.draw_lengths(w, seed=0)
+    heads = w.heads
+    g = torch.Generator(device=DEV).manual_seed(4)
+    total = int(lengths.sum())
+    q, k, v, d_out = (torch.randn(total, heads, 64, generator=g, device=DEV).to(torch.bfloat16) for _ in range(4))
+    cu = W.cu_seqlens_from_lengths(lengths).to(DEV)
+    max_len = int(lengths.max())
+
+    def run(qs, ks, vs, gs, cus, max_l):
+        qs, ks, vs = (t.detach().clone().requires_grad_(True) for t in (qs, ks, vs))
+        out = nanobrain_b200.sdpa_varlen(qs, ks, vs, cus, cus, max_l, max_l)
+        out.backward(gs)
+        ops.check_status()
+        return out.detach(), qs.grad, ks.grad, vs.grad
+
+    full = run(q, k, v, d_out, cu, max_len)
+    shard = W.shard_lengths(lengths, 3, 8)                          # rank 3 of 8
+    a, b = int(cu[3 * 32]), int(cu[4 * 32])
+    cu_s = W.cu_seqlens_from_lengths(shard).to(DEV)
+    part = run(q[a:b], k[a:b], v[a:b], d_out[a:b], cu_s, int(shard.max()))
+    assert torch.equal(part[0], full[0][a:b]) and torch.equal(part[2], full[2][a:b]) and torch.equal(part[3], full[3][a:b])
+    assert (part[1].float() - full[1][a:b].float()).abs().max() <= 2e-2    # fp32 dQ additions arrive in any order
+    for i in (0, 255):
+        s0, s1 = int(cu[i]), int(cu[i + 1])
+        sl = lambda t: t[s0:s1].transpose(0, 1)
+        ref = math_sdpa_fp32(sl(q), sl(k), sl(v), sl(d_out))
+        for name, got, want in zip(("out", "dq", "dk", "dv"), full, ref):
+            close_abs(f"vitb_encoder_varlen_b256 sequence {i}", name, got[s0:s1].transpose(0, 1), want)
+    ones = torch.ones_like(v)
+    out1 = nanobrain_b200.sdpa_varlen(q, k, ones, cu, cu, max_len, max_len)
+    ops.check_status()
+    assert (out1.float() - 1).abs().max() <= 8e-3
