@@ -26,8 +26,9 @@
 //   attn_bwd_epilogue_kernel : dQ = bf16(scale * accumulator). HBM-bound.
 //
 // Packed mode: block 0 of the prologue also builds the scheduler's work list of key tiles
-// (sched_kernel.cuh) and the main kernel's grid is items x heads (the heads of one item adjacent). A ragged tile is computed at full
-// width and masked: rows of the NEXT packed sequence that it brings into shared memory are
+// (sched_kernel.cuh) and the main kernel's grid is items x heads (the heads of one item adjacent).
+// A ragged tile is computed at full width and masked: rows of the NEXT packed sequence that it
+// brings into shared memory are
 // multiplied by exact zeros of P^T / dS^T. For finite data that is exact; if the next sequence's
 // first rows hold Inf or NaN, 0 x Inf makes this sequence's gradients NaN as well (the forward
 // kernel clears such rows and keeps sequences isolated; measured here, clearing them in this
