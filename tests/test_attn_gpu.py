@@ -479,3 +479,23 @@ def test_scaling_config_global_batch_256_by_properties_and_shards():
     out1 = nanobrain_b200.sdpa_varlen(q, k, ones, cu, cu, max_len, max_len)
     ops.check_status()
     assert (out1.float() - 1).abs().max() <= 8e-3
+
+
+@pytest.mark.parametrize("boost_from", [128, 256, 300])
+def test_forward_refreshes_its_offset_when_later_key_tiles_dominate(boost_from):
+    # After the first key tile the forward does not compute a row max: it exponentiates against the
+    # running offset and redoes a tile only if its row sum shows that an exponent ran far above it.
+    # Keys from `boost_from` on are 25x larger, so the scores of later tiles exceed the first tile's
+    # by hundreds in the log2 domain: the redo + rescale path must give the oracle's result.
+    g = torch.Generator().manual_seed(boost_from)
+    q = torch.randn(1, 2, 200, 64, generator=g)
+    k = torch.randn(1, 2, 520, 64, generator=g)
+    v = torch.randn(1, 2, 520, 64, generator=g)
+    d_out = torch.randn(1, 2, 200, 64, generator=g)
+    k[:, :, boost_from:] *= 25.0
+    q, k, v, d_out = rounded(q, k, v, d_out)
+    want = O.sdpa_fwd_bwd(q.numpy(), k.numpy(), v.numpy(), d_out.numpy())
+    out, dq, dk, dv = run_dense(q, k, v, d_out)
+    close("out", out, want[0]), close("dq", dq, want[2]), close("dk", dk, want[3]), close("dv", dv, want[4])
+    _, lse = ops.sdpa_fwd(q.to(DEV, torch.bfloat16), k.to(DEV, torch.bfloat16), v.to(DEV, torch.bfloat16), 0.125)
+    np.testing.assert_allclose(lse.cpu().numpy(), want[1], rtol=2e-3, atol=2e-3)
