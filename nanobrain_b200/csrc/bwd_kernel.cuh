@@ -2,8 +2,8 @@
 //
 //   attn_bwd_prologue_kernel : delta[row] = sum_d dO[row,d] * O[row,d] (warp-shuffle row dot) and
 //                              clears the fp32 dQ accumulator. HBM-bound.
-//   attn_bwd_kernel          : one CTA owns one 128-row K/V tile of one (sequence, head) and walks
-//                              the sequence's queries in 128-row tiles. Everything is computed
+//   attn_bwd_kernel          : a work unit is one 128-row K/V tile of one (sequence, head), walked
+//                              over the sequence's queries in 128-row steps. Everything is computed
 //                              transposed so that a thread owns a key row (tensor-memory lane):
 //                                S^T  = K Q^T                       (tcgen05, smem x smem)
 //                                dP^T = V dO^T                      (tcgen05, smem x smem)
@@ -14,19 +14,36 @@
 //                                dQ   = dS K                        (same dS bytes read MN-major)
 //                              dQ tiles are added into the fp32 accumulator with TMA add-reductions
 //                              because every K/V tile of a sequence contributes to every dQ row.
+//                              CTAs are persistent (one per SM): each walks its share of the work
+//                              units and the step pipeline runs on through the boundary between
+//                              two units -- K is double-buffered, V is reloaded as soon as the
+//                              unit's last dP^T MMA has read it, dV / dK leave through the drain
+//                              warps while the next unit's first steps run -- so a unit's start-up
+//                              and tail (a third of a CTA's life on ~800-token sequences) overlap
+//                              its neighbours' steps.
 //                              Warp roles (640 threads): warps 0-7 are two compute warpgroups that
-//                              split the 128 query columns of a tile (64 each); warps 8-11 are
+//                              split the 128 query columns of a step (64 each); warps 8-11 are
 //                              four MMA issuers (S^T/dP^T, dV, dK, dQ: one elected thread each --
 //                              a single thread can issue a tcgen05.mma only every ~55 cycles, so
-//                              the 32 MMAs of a tile need several issuers to keep the tensor pipe
+//                              the 32 MMAs of a step need several issuers to keep the tensor pipe
 //                              fed); warps 12-15 drain the dQ tiles (one tensor-memory lane
-//                              quadrant each) into the accumulator; warp 16 drives TMA and stages
-//                              LSE/delta rows (warps 17-19 only complete its warpgroup for the
-//                              register re-partitioning).
+//                              quadrant each) into the accumulator and, at the end of a unit, dV
+//                              and dK into their tensors; warp 16 drives TMA; warp 17 stages the
+//                              steps' LSE/delta rows and control words (warps 18-19 only complete
+//                              its warpgroup for the register re-partitioning). The loaders and
+//                              the drain warps read the work list; the compute warps and the
+//                              issuers learn about a step from its control word alone.
+//                              Code size is a first-order concern here: five roles' loops run at
+//                              the same time and have to share the SM's instruction cache (at
+//                              67 KB of code its hit rate was 68 % and instruction fetch was the
+//                              top stall; at 48 KB it is above 93 %). Hence the compact wait loop,
+//                              rolled MMA-issue loops, divisions by multiply-high, and the compute
+//                              role as a function that is not inlined.
 //   attn_bwd_epilogue_kernel : dQ = bf16(scale * accumulator). HBM-bound.
 //
 // Packed mode: block 0 of the prologue also builds the scheduler's work list of key tiles
-// (sched_kernel.cuh) and the main kernel's grid is items x heads (the heads of one item adjacent).
+// (sched_kernel.cuh); the main kernel's work units are list entries x heads (the heads of one entry
+// adjacent), dealt to the CTAs in the list's order of decreasing cost.
 // A ragged tile is computed at full width and masked: rows of the NEXT packed sequence that it
 // brings into shared memory are
 // multiplied by exact zeros of P^T / dS^T. For finite data that is exact; if the next sequence's
@@ -40,6 +57,26 @@
 #include "ptx.cuh"
 
 namespace nb {
+
+// Division of a number below 2^31 by a fixed divisor as a multiply-high and a shift (the divisor's
+// magic numbers come from the host). The work-index split is inlined in four warp roles, and an
+// integer division routine in each of them is code the instruction cache has no room for.
+struct FastDiv {
+  uint32_t mul, shr, div;
+  __device__ __forceinline__ uint32_t quot(uint32_t n) const { return div == 1u ? n : __umulhi(n, mul) >> shr; }
+};
+inline FastDiv make_fast_div(uint32_t d) {
+  FastDiv f;
+  f.div = d, f.mul = 0, f.shr = 0;
+  if (d > 1) {
+    uint32_t lg = 0;
+    while ((1ull << lg) < d) ++lg;  // ceil(log2 d)
+    const uint64_t p = 31 + lg;
+    f.mul = uint32_t(((1ull << p) + d - 1) / d);
+    f.shr = uint32_t(p - 32);
+  }
+  return f;
+}
 
 struct BwdParams {
   const __nv_bfloat16 *o, *d_o;
@@ -55,6 +92,9 @@ struct BwdParams {
   SchedParams sched;      // packed mode: what block 0 of the prologue builds (items == NULL: nothing)
   int32_t batch, heads;
   int32_t lq, lk;
+  int32_t n_work;  // work units of the main kernel: key tiles x heads x sequences, or list entries x heads
+  int32_t n_kt;    // dense mode: key tiles per (sequence, head)
+  FastDiv div_heads, div_n_kt;  // the main kernel splits a work index without a division routine
   int64_t total_q, total_k;
   float scale, scale_log2;
   int32_t* status;
@@ -141,9 +181,11 @@ __global__ void __launch_bounds__(256) attn_bwd_epilogue_kernel(const BwdParams 
 // ----------------------------------------------------------------------------------------
 constexpr int kBwdThreads = 640;
 constexpr int kBwdStages = 3;  // Q/dO ring
-// K, V, 3x(Q, dO), dS (two 64-column halves), fp32 dQ staging (two 32-column halves) + LSE/delta
-// stages + alignment slack
-constexpr int kBwdSmemBytes = (2 + 2 * kBwdStages + 4) * kTileBytes + kBwdStages * 2 * kTile * 4 + 1024;
+constexpr int kBwdOutStageBytes = 8192;  // dK/dV read-out: 2 KB per drain warp
+// K (two buffers), V, 3x(Q, dO), dS (two 64-column halves), fp32 dQ staging (two 32-column halves),
+// the dK/dV read-out staging, LSE/delta stages, the steps' control words and alignment slack
+constexpr int kBwdSmemBytes =
+    (3 + 2 * kBwdStages + 4) * kTileBytes + kBwdOutStageBytes + kBwdStages * 2 * kTile * 4 + 32 + 1024;
 constexpr int kBwdTmemCols = 512;  // S^T 0, dP^T 128, P^T 256, dV 320, dK 384, dQ 448
 // Register re-partitioning. The CTA launches with 640 threads x 96 registers (the most the
 // register file allows); setmaxnreg only moves registers inside that allocation, so the budget
@@ -160,22 +202,235 @@ static_assert(256 * kBwdComputeRegs + 128 * (kBwdIssuerRegs + kBwdDrainRegs + kB
                   kBwdThreads * kBwdLaunchRegs, "register budget");
 
 enum BwdBar : int {
-  kBarKvFull = 0,
-  kBarQdoFull = 1,                       // [kBwdStages]
+  kBarKFull = 0,                            // [2] K is double-buffered across a CTA's work items
+  kBarKFree = 2,                            // [2] the item's last dQ MMA has read K
+  kBarVFull = 4,
+  kBarVFree,                                // the item's last dP^T MMA has read V
+  kBarQdoFull,                              // [kBwdStages] TMA issue + LSE/delta staged
   kBarQdoEmpty = kBarQdoFull + kBwdStages,  // [kBwdStages], 3 arrivals: S/dP, dV and dK issuers
   kBarSFull = kBarQdoEmpty + kBwdStages,
   kBarSFree,    // 8 arrivals (one per compute warp)
   kBarDpFull,
   kBarDpFree,   // 8
   kBarPFull,    // 8
-  kBarPtFree,   // dV MMAs of the tile have consumed P^T
+  kBarPtFree,   // dV MMAs of the step have consumed P^T
   kBarDsFull,   // 8 arrivals
   kBarDsFree,   // 2 arrivals: dK and dQ issuers
   kBarDqFull,
   kBarDqFree,   // 4 (dQ drain warps)
+  kBarDvDone,   // the item's last dV MMA is complete
   kBarDkDone,
+  kBarDvOut,    // 4: the drain warps have read the item's dV accumulator
+  kBarDkOut,    // 4
   kBwdNumBars
 };
+
+// One unit of a CTA's work: a 128-row K/V tile of one (sequence, head).
+struct BwdWork {
+  int n_q;  // query tiles to walk; 0: keys without queries (dK = dV = 0); -1: no more work
+  int kt, h, b, bcoord;
+  int k_begin, lk, q_begin, lq;
+};
+
+// CTAs are persistent: CTA c of G takes the work units c, 2G-1-c, 2G+c, ... ("snake" order over
+// rounds of G). The list is ordered by decreasing cost, so this hands every CTA nearly the same
+// total, without a shared counter: every warp role of a CTA walks the same sequence on its own.
+__device__ __forceinline__ uint32_t bwd_work_index(uint32_t round) {
+  const uint32_t c = (round & 1u) ? gridDim.x - 1u - blockIdx.x : blockIdx.x;
+  return round * gridDim.x + c;
+}
+
+__device__ __forceinline__ BwdWork bwd_work(const BwdParams& p, uint32_t round) {
+  BwdWork w;
+  w.n_q = -1, w.kt = 0, w.h = 0, w.b = 0, w.bcoord = 0, w.k_begin = 0, w.lk = 0, w.q_begin = 0, w.lq = 0;
+  const uint32_t g = bwd_work_index(round);
+  if (g >= uint32_t(p.n_work)) return w;
+  if (p.cu_q != nullptr) {
+    // One 32-byte read tells all about the item (the sequence index `batch` stands for the rows past
+    // the last sequence: keys without queries). Unused entries sit at the end of the list.
+    const uint32_t idx = p.div_heads.quot(g);
+    const SchedItem item = sched_load(p.items, idx);
+    if (item.seq < 0) return w;
+    w.h = int(g - idx * uint32_t(p.heads));
+    w.b = item.seq, w.kt = item.tile;
+    w.k_begin = item.own_begin, w.lk = item.own_len;
+    w.q_begin = item.other_begin, w.lq = item.other_len;
+  } else {
+    const uint32_t t = p.div_n_kt.quot(g);
+    w.kt = int(g - t * uint32_t(p.n_kt));
+    w.b = w.bcoord = int(p.div_heads.quot(t));
+    w.h = int(t - uint32_t(w.b) * uint32_t(p.heads));
+    w.lk = p.lk, w.lq = p.lq;
+  }
+  w.n_q = (w.lq + kTile - 1) / kTile;
+  return w;
+}
+
+// Query tile an item starts at. Concurrent CTAs work on the key tiles of one (sequence, head) and
+// all add into the same dQ tiles, so they start at different ones: key tile kt at query tile kt,
+// and where there are more key tiles than query tiles at a tile picked by a multiplicative hash
+// (a multiply-high maps it into [0, n_q) without a division routine).
+__device__ __forceinline__ int bwd_first_tile(int kt, int n_q) {
+  return kt < n_q ? kt : int(__umulhi(uint32_t(kt) * 0x9E3779B9u, uint32_t(n_q)));
+}
+
+// Running position of a role in the CTA's stream of steps: step count, Q/dO stage and the phase of
+// that stage's barriers. Steps run on through the boundaries between work items.
+struct BwdStepPos {
+  uint32_t s = 0, qs = 0, qph = 0;
+  __device__ __forceinline__ void advance() {
+    ++s;
+    if (++qs == uint32_t(kBwdStages)) qs = 0, qph ^= 1u;
+  }
+};
+
+// Control word of a step, staged with the step's LSE/delta rows (one per Q/dO stage). The compute
+// warps and the MMA issuers learn everything about a step from it, so they never read the work
+// list or leave their step loops: between two items of a persistent CTA they would otherwise run
+// cold code behind a global-memory read (measured: 1500-3000 cycles per item boundary).
+enum BwdCtrl : uint32_t {
+  kCtrlFirst = 1u,  // first step of a work item
+  kCtrlLast = 2u,   // last step of a work item
+  kCtrlKb = 4u,     // which K buffer the item uses
+  kCtrlStop = 8u,   // no step: the CTA's work has ended
+  // bits 8-15: live query columns of the step's tile (1..128); bits 16-23: live key rows of the item's tile
+};
+
+// The compute warps' role: for every step of the CTA, P^T from S^T, then dS^T from dP^T.
+// Not inlined on purpose: compiled by itself the step body keeps its instruction schedule (it sits
+// at the compute warps' 168-register cap, and inlined into the kernel it came out 10-60 % slower
+// whenever the code around it changed).
+__device__ __noinline__ void bwd_compute_role(const uint32_t bar0, int* abort_flag, int32_t* status,
+                                              const uint32_t tmem_base, const float* sLse, const float* sDelta,
+                                              const volatile uint32_t* sCtrl, uint8_t* sDS_ptr,
+                                              const float scale_log2) {
+  const int warp = threadIdx.x >> 5;
+  const int w = warp >> 2;                       // warpgroup: query columns [64w, 64w+64)
+  const int krow_in_tile = threadIdx.x & 127;    // key row of this thread = tensor-memory lane
+  const uint32_t tm_lane = tmem_base + (uint32_t((warp & 3) * 32) << 16);
+  uint8_t* ds_half = sDS_ptr + w * kTileBytes;
+  BwdStepPos pos;
+  for (;; pos.advance()) {
+  const uint32_t s = pos.s, qs = pos.qs, qph = pos.qph;
+  auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
+  const int lane = threadIdx.x & 31;
+  const uint32_t tm_s = tm_lane, tm_dp = tm_lane + 128, tm_pt = tm_lane + 256;
+  const uint64_t scale2 = pack_f32x2(scale_log2, scale_log2);
+  const float4* lse4 = reinterpret_cast<const float4*>(sLse + qs * kTile + 64 * w);   // -lse (log2)
+  const float4* dl4 = reinterpret_cast<const float4*>(sDelta + qs * kTile + 64 * w);  // -delta
+  uint64_t pf[32];  // P^T values of this thread as packed fp32 pairs
+
+  bool pt_ok, dp_ok;
+  // ---- phase A: P^T = exp2(S^T * scale_log2 - lse) ----
+  mbar_wait2(bar(kBarQdoFull + qs), qph, bar(kBarSFull), s & 1, abort_flag, status);
+  const uint32_t ctrl = sCtrl[qs];
+  if ((ctrl & kCtrlStop) || *reinterpret_cast<volatile int*>(abort_flag)) break;
+  // Key rows past the end of the sequence must not contribute to dQ; on the ragged last query tile
+  // this warpgroup's half has fewer than 64 live columns.
+  const bool zero_row = krow_in_tile >= int((ctrl >> 16) & 0xFFu);
+  const int valid_cols = int((ctrl >> 8) & 0xFFu) - 64 * w;
+  tc_fence_after();
+  {
+    uint32_t ra[32], rb[32];
+    tmem_ld32(tm_s + 64 * w, ra);
+    tmem_ld32(tm_s + 64 * w + 32, rb);
+    tmem_wait_ld();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(kBarSFree));
+    // Poll the barriers needed after the exponentials now; the polls' latency overlaps them.
+    pt_ok = s > 0 ? mbar_try_wait(bar(kBarPtFree), (s - 1) & 1) : true;
+    dp_ok = mbar_try_wait(bar(kBarDpFull), s & 1);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t* src = i < 8 ? &ra[4 * i] : &rb[4 * (i - 8)];
+      const float4 l = lse4[i];
+      float x0, x1, x2, x3;
+      unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(src[0]), __uint_as_float(src[1])), scale2,
+                             pack_f32x2(l.x, l.y)), x0, x1);
+      unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(src[2]), __uint_as_float(src[3])), scale2,
+                             pack_f32x2(l.z, l.w)), x2, x3);
+      pf[2 * i] = pack_f32x2(fast_exp2(x0), fast_exp2(x1));
+      // Every other second pair goes to the FMA pipe: the exponentials are this phase's
+      // bottleneck (both warps of an SM sub-partition run it together on one MUFU unit).
+      if (i & 1) pf[2 * i + 1] = exp2_poly_f32x2(pack_f32x2(x2, x3));
+      else pf[2 * i + 1] = pack_f32x2(fast_exp2(x2), fast_exp2(x3));
+    }
+  }
+  if (zero_row) {
+    // Key rows past the end of the sequence must not contribute to dQ.
+#pragma unroll
+    for (int i = 0; i < 32; ++i) pf[i] = 0ull;
+  }
+  if (valid_cols < 64) {
+    // Query columns past the end of the sequence: the hardware exponential already gave exactly 0
+    // for their -inf argument, but the polynomial's clamp gave 2^-126. Zero those too (the second
+    // pair of every odd group of four columns), so that nothing at all is added to the dQ rows of
+    // the next packed sequence.
+#pragma unroll
+    for (int i = 1; i < 16; i += 2) {
+      float a0, a1;
+      unpack_f32x2(pf[2 * i + 1], a0, a1);
+      pf[2 * i + 1] = pack_f32x2(4 * i + 2 < valid_cols ? a0 : 0.f, 4 * i + 3 < valid_cols ? a1 : 0.f);
+    }
+  }
+  if (s > 0) {
+    if (!pt_ok) mbar_wait(bar(kBarPtFree), (s - 1) & 1, abort_flag, status);
+    tc_fence_after();
+  }
+  {
+    uint32_t pk[16];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float a0, a1;
+        unpack_f32x2(pf[16 * c + i], a0, a1);
+        pk[i] = pack_bf16(a0, a1);
+      }
+      tmem_st16(tm_pt + 32 * w + 16 * c, pk);
+    }
+  }
+
+  // ---- middle: pull dP^T of this tile out of tensor memory ----
+  uint32_t ra[32], rb[32];
+  if (!dp_ok) mbar_wait(bar(kBarDpFull), s & 1, abort_flag, status);
+  tc_fence_after();
+  const bool ds_ok = s > 0 ? mbar_try_wait(bar(kBarDsFree), (s - 1) & 1) : true;
+  tmem_ld32(tm_dp + 64 * w, ra);
+  tmem_ld32(tm_dp + 64 * w + 32, rb);
+  tmem_wait_ld();
+  tmem_wait_st();
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) {
+    mbar_arrive(bar(kBarPFull));
+    mbar_arrive(bar(kBarDpFree));
+  }
+
+  // ---- phase B: dS^T = P^T o (dP^T - delta) -> shared memory ----
+  if (!ds_ok) mbar_wait(bar(kBarDsFree), (s - 1) & 1, abort_flag, status);
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = query columns [8c, 8c+8) of this half
+    const uint32_t* src = c < 4 ? &ra[8 * c] : &rb[8 * (c - 4)];
+    const float4 d0 = dl4[2 * c], d1 = dl4[2 * c + 1];
+    const uint64_t nd[4] = {pack_f32x2(d0.x, d0.y), pack_f32x2(d0.z, d0.w), pack_f32x2(d1.x, d1.y),
+                            pack_f32x2(d1.z, d1.w)};
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint64_t dp2 = pack_f32x2(__uint_as_float(src[2 * i]), __uint_as_float(src[2 * i + 1]));
+      float a0, a1;
+      unpack_f32x2(mul_f32x2(pf[4 * c + i], add_f32x2(dp2, nd[i])), a0, a1);
+      o[i] = pack_bf16(a0, a1);
+    }
+    *reinterpret_cast<uint4*>(ds_half + swz128(krow_in_tile, c)) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar(kBarDsFull));
+  }
+}
 
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -189,49 +444,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
 
   // delta, the cleared dQ accumulator and the work list come from the prologue kernel.
   pdl_wait();
   pdl_launch_dependents();
 
-  int q_begin = 0, k_begin = 0, lq = p.lq, lk = p.lk, bcoord = b;
-  if (p.cu_q != nullptr) {
-    // One read tells the CTA everything about its item (the sequence index `batch` stands for the
-    // rows past the last sequence: keys without queries, which get dK = dV = 0).
-    const SchedItem item = sched_load(p.items, blockIdx.x / uint32_t(p.heads));
-    if (item.seq < 0) return;
-    h = blockIdx.x % uint32_t(p.heads);
-    b = item.seq;
-    kt = item.tile;
-    k_begin = item.own_begin;
-    lk = item.own_len;
-    q_begin = item.other_begin;
-    lq = item.other_len;
-    bcoord = 0;
-  }
-  const int k_row0 = kt * kTile;
-  if (k_row0 >= lk) return;
-  const int n_q = (lq + kTile - 1) / kTile;
-
   uint8_t* smem_al = smem_raw + (((smem_u32(smem_raw) + 1023u) & ~1023u) - smem_u32(smem_raw));
   const uint32_t smem_base = smem_u32(smem_al);
-  const uint32_t sK = smem_base;
-  const uint32_t sV = smem_base + 1 * kTileBytes;
-  auto sQ = [&](int s) { return smem_base + (2 + 2 * s) * kTileBytes; };
-  auto sDO = [&](int s) { return smem_base + (3 + 2 * s) * kTileBytes; };
-  constexpr int kDsTile0 = 2 + 2 * kBwdStages;
+  auto sK = [&](uint32_t kb) { return smem_base + kb * kTileBytes; };
+  const uint32_t sV = smem_base + 2 * kTileBytes;
+  auto sQ = [&](uint32_t s) { return smem_base + (3 + 2 * s) * kTileBytes; };
+  auto sDO = [&](uint32_t s) { return smem_base + (4 + 2 * s) * kTileBytes; };
+  constexpr int kDsTile0 = 3 + 2 * kBwdStages;
   const uint32_t sDS = smem_base + kDsTile0 * kTileBytes;  // 32 KB bf16: q columns 0..63 | 64..127
   uint8_t* sDS_ptr = smem_al + kDsTile0 * kTileBytes;
   uint8_t* sDQ_ptr = smem_al + (kDsTile0 + 2) * kTileBytes;  // 32 KB fp32: d columns 0..31 | 32..63
-  float* sLse = reinterpret_cast<float*>(smem_al + (kDsTile0 + 4) * kTileBytes);  // [stages][128], log2 domain
-  float* sDelta = sLse + kBwdStages * kTile;                                      // [stages][128]
+  uint8_t* sOut_ptr = smem_al + (kDsTile0 + 4) * kTileBytes;  // dK/dV read-out staging
+  float* sLse = reinterpret_cast<float*>(sOut_ptr + kBwdOutStageBytes);  // [stages][128], log2 domain
+  float* sDelta = sLse + kBwdStages * kTile;                             // [stages][128]
+  uint32_t* sCtrl = reinterpret_cast<uint32_t*>(sDelta + kBwdStages * kTile);  // [stages], see BwdCtrl
+  uint32_t* sCtrlQ = sCtrl + 4;  // [4], indexed by step & 3: the dQ issuer's copy (it does not hold the stage)
 
   const uint32_t bar0 = smem_u32(&bars[0]);
   auto bar = [&](int i) { return bar0 + 8u * uint32_t(i); };
 
-  // The producer's own thread initialises the barriers, so it can request K, V and the first Q/dO
-  // tiles at once; the other threads meet the barriers only after the __syncthreads below.
   if (tid == 16 * 32) {
     tma_prefetch_desc(&tmap_k);
     tma_prefetch_desc(&tmap_q);
@@ -242,22 +478,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       uint32_t count = 1;
       if (i >= kBarQdoFull && i < kBarQdoFull + kBwdStages) count = 2;  // TMA issue + LSE/delta staged
       if (i >= kBarQdoEmpty && i < kBarQdoEmpty + kBwdStages) count = 3;
-      if (i == kBarSFree || i == kBarDpFree || i == kBarPFull) count = 8;
-      if (i == kBarDqFree) count = 4;
-      if (i == kBarDsFull) count = 8;
+      if (i == kBarSFree || i == kBarDpFree || i == kBarPFull || i == kBarDsFull) count = 8;
+      if (i == kBarDqFree || i == kBarDvOut || i == kBarDkOut) count = 4;
       if (i == kBarDsFree) count = 2;
       mbar_init(bar(i), count);
     }
     fence_mbar_init();
-    if (n_q > 0) {
-      const int jt0 = kt % n_q;
-      mbar_arrive_expect_tx(bar(kBarKvFull), 2 * kTileBytes);
-      tma_load_4d(sK, &tmap_k, bar(kBarKvFull), 0, k_begin + k_row0, h, bcoord);
-      tma_load_4d(sV, &tmap_v, bar(kBarKvFull), 0, k_begin + k_row0, h, bcoord);
-      mbar_arrive_expect_tx(bar(kBarQdoFull), 2 * kTileBytes);
-      tma_load_4d(sQ(0), &tmap_q, bar(kBarQdoFull), 0, q_begin + jt0 * kTile, h, bcoord);
-      tma_load_4d(sDO(0), &tmap_do, bar(kBarQdoFull), 0, q_begin + jt0 * kTile, h, bcoord);
-    }
   }
   if (warp == 8) {
     tmem_alloc(smem_u32(&tmem_base_slot), kBwdTmemCols);
@@ -273,337 +499,360 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
   constexpr uint32_t kIdescS = make_idesc(128, 128, 0, 0);   // K-major x K-major, N = 128
   constexpr uint32_t kIdescKN = make_idesc(128, 64, 0, 1);   // A K-major / tensor memory, B MN-major
   constexpr uint32_t kIdescNN = make_idesc(128, 64, 1, 1);   // A MN-major, B MN-major
-  const int64_t stat_base = p.cu_q != nullptr ? int64_t(h) * p.total_q + q_begin : (int64_t(b) * p.heads + h) * p.lq;
+  const bool packed = p.cu_q != nullptr;
 
-  if (n_q > 0) {
-    if (warp >= 16) {
-      // ---------------- TMA producer + LSE/delta staging (warp 16; 17-19 idle) ----------------
-      setmaxnreg_dec<kBwdLoaderRegs>();
-      if (warp == 16) {
-      for (int j = 0; j < n_q; ++j) {
-        const int qs = j % kBwdStages;
-        const int jt = (j + kt) % n_q;  // staggered start: concurrent CTAs touch different dQ tiles
-        // The tile's LSE/delta rows are requested before the wait for a free stage, so that this
-        // latency does not sit between a stage becoming free and becoming full again. They are
-        // staged negated: -lse in the log2 domain and -delta. Rows past the end of the sequence get
-        // -lse = -inf, which makes their P^T column 0.
-        float l2[4], dl[4];
+  if (warp >= 16) {
+    setmaxnreg_dec<kBwdLoaderRegs>();
+    if (warp == 16) {
+      // ---------------- TMA producer (one lane) ----------------
+      // K of the next item goes into the other K buffer; V is reloaded as soon as the item's last
+      // dP^T MMA has read it; Q/dO tiles run through the ring without regard to item boundaries.
+      if (lane == 0) {
+        BwdStepPos pos;
+        uint32_t ni = 0;  // items with queries so far
+#pragma unroll 1
+        for (uint32_t round = 0;; ++round) {
+          const BwdWork wk = bwd_work(p, round);
+          if (wk.n_q < 0) break;
+          if (wk.n_q == 0) continue;
+          const uint32_t kb = ni & 1u;
+          const int krow = wk.k_begin + wk.kt * kTile;
+          if (ni >= 2) mbar_wait(bar(kBarKFree + kb), ((ni >> 1) - 1) & 1, &abort_flag, p.status);
+          mbar_arrive_expect_tx(bar(kBarKFull + kb), kTileBytes);
+          tma_load_4d(sK(kb), &tmap_k, bar(kBarKFull + kb), 0, krow, wk.h, wk.bcoord);
+          int jt = bwd_first_tile(wk.kt, wk.n_q);
+#pragma unroll 1
+          for (int j = 0; j < wk.n_q; ++j) {
+            if (pos.s >= uint32_t(kBwdStages))
+              mbar_wait(bar(kBarQdoEmpty + pos.qs), pos.qph ^ 1u, &abort_flag, p.status);
+            mbar_arrive_expect_tx(bar(kBarQdoFull + pos.qs), 2 * kTileBytes);
+            tma_load_4d(sQ(pos.qs), &tmap_q, bar(kBarQdoFull + pos.qs), 0, wk.q_begin + jt * kTile, wk.h, wk.bcoord);
+            tma_load_4d(sDO(pos.qs), &tmap_do, bar(kBarQdoFull + pos.qs), 0, wk.q_begin + jt * kTile, wk.h,
+                        wk.bcoord);
+            if (j == 0) {
+              if (ni >= 1) mbar_wait(bar(kBarVFree), (ni - 1) & 1, &abort_flag, p.status);
+              mbar_arrive_expect_tx(bar(kBarVFull), kTileBytes);
+              tma_load_4d(sV, &tmap_v, bar(kBarVFull), 0, krow, wk.h, wk.bcoord);
+            }
+            pos.advance();
+            jt = jt + 1 == wk.n_q ? 0 : jt + 1;
+          }
+          ++ni;
+        }
+        // One more stage carries the stop mark (no data).
+        if (pos.s >= uint32_t(kBwdStages)) mbar_wait(bar(kBarQdoEmpty + pos.qs), pos.qph ^ 1u, &abort_flag, p.status);
+        mbar_arrive(bar(kBarQdoFull + pos.qs));
+      }
+    } else if (warp == 17) {
+      // ---------------- LSE/delta staging and the steps' control words ----------------
+      // A step's rows are requested before the wait for a free stage, so that this latency does not
+      // sit between a stage becoming free and becoming full again. They are staged negated: -lse in
+      // the log2 domain and -delta. Rows past the end of the sequence get -lse = -inf, which makes
+      // their P^T column 0.
+      BwdStepPos pos;
+      uint32_t ni = 0;
+#pragma unroll 1
+      for (uint32_t round = 0;; ++round) {
+        const BwdWork wk = bwd_work(p, round);
+        if (wk.n_q < 0) break;
+        if (wk.n_q == 0) continue;
+        const int rows_live = min(wk.lk - wk.kt * kTile, kTile);
+        const int64_t stat_base =
+            packed ? int64_t(wk.h) * p.total_q + wk.q_begin : (int64_t(wk.b) * p.heads + wk.h) * p.lq;
+        int jt = bwd_first_tile(wk.kt, wk.n_q);
+#pragma unroll 1
+        for (int j = 0; j < wk.n_q; ++j) {
+          float l2[4], dl[4];
 #pragma unroll
-        for (int r4 = 0; r4 < 4; ++r4) {
-          const int r = jt * kTile + r4 * 32 + lane;
-          l2[r4] = -INFINITY, dl[r4] = 0.f;
-          if (r < lq) {
-            l2[r4] = p.lse[stat_base + r] * -1.4426950408889634f;
-            dl[r4] = -p.delta[stat_base + r];
+          for (int r4 = 0; r4 < 4; ++r4) {
+            const int r = jt * kTile + r4 * 32 + lane;
+            l2[r4] = -INFINITY, dl[r4] = 0.f;
+            if (r < wk.lq) {
+              l2[r4] = p.lse[stat_base + r] * -1.4426950408889634f;
+              dl[r4] = -p.delta[stat_base + r];
+            }
+          }
+          if (pos.s >= uint32_t(kBwdStages) && lane == 0)
+            mbar_wait(bar(kBarQdoEmpty + pos.qs), pos.qph ^ 1u, &abort_flag, p.status);
+          __syncwarp();
+#pragma unroll
+          for (int r4 = 0; r4 < 4; ++r4) {
+            sLse[pos.qs * kTile + r4 * 32 + lane] = l2[r4];
+            sDelta[pos.qs * kTile + r4 * 32 + lane] = dl[r4];
+          }
+          if (lane == 0) {
+            const int cols_live = min(wk.lq - jt * kTile, kTile);
+            const uint32_t ctrl = (j == 0 ? kCtrlFirst : 0u) | (j == wk.n_q - 1 ? kCtrlLast : 0u) |
+                                  ((ni & 1u) ? kCtrlKb : 0u) | (uint32_t(cols_live) << 8) |
+                                  (uint32_t(rows_live) << 16);
+            sCtrl[pos.qs] = ctrl;
+            sCtrlQ[pos.s & 3u] = ctrl;
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(kBarQdoFull + pos.qs));
+          pos.advance();
+          jt = jt + 1 == wk.n_q ? 0 : jt + 1;
+        }
+        ++ni;
+      }
+      if (lane == 0) {
+        if (pos.s >= uint32_t(kBwdStages)) mbar_wait(bar(kBarQdoEmpty + pos.qs), pos.qph ^ 1u, &abort_flag, p.status);
+        sCtrl[pos.qs] = kCtrlStop;
+        sCtrlQ[pos.s & 3u] = kCtrlStop;
+        mbar_arrive(bar(kBarQdoFull + pos.qs));
+      }
+    }
+  } else if (warp >= 12) {
+    // ---------------- drain warps: dQ tiles every step, dV and dK at the end of an item ----------------
+    // Warp 12+q owns tensor-memory lane quadrant q. dQ: it stages its 32 rows (two 32-column
+    // halves, 128-byte swizzled rows) in shared memory and one lane issues the TMA add-reductions,
+    // so only warp-level synchronisation is needed and L2 receives whole 128-byte lines. Rows past
+    // the end of the sequence are staged as exact zeros, so adding them is harmless. dV / dK: when
+    // the item's last MMA into the accumulator is complete the warp turns its 32 rows into bf16,
+    // 32 columns at a time through a 2 KB scratch area, and stores them four lanes per 64-byte
+    // half row; the issuers start the next item's first dV / dK MMA only after that.
+    setmaxnreg_dec<kBwdDrainRegs>();
+    const int quad = warp & 3;
+    const uint32_t lane_off = uint32_t(quad * 32) << 16;
+    uint8_t* stage = sDQ_ptr + quad * 4096;
+    uint8_t* ostage = sOut_ptr + quad * (kBwdOutStageBytes / 4);
+    uint32_t s = 0, ni = 0;
+#pragma unroll 1
+    for (uint32_t round = 0;; ++round) {
+      int n_q;
+      {
+        // The step loop keeps only what it needs of the work item (this role has 56 registers).
+        const BwdWork wk = bwd_work(p, round);
+        n_q = wk.n_q;
+        if (n_q < 0) break;
+        if (n_q > 0) {
+          const int h = wk.h;
+          int row = (packed ? 0 : wk.b * p.lq) + wk.q_begin + quad * 32 + bwd_first_tile(wk.kt, n_q) * kTile;
+          const int row_end = (packed ? 0 : wk.b * p.lq) + wk.q_begin + quad * 32 + n_q * kTile;
+#pragma unroll 1
+          for (int j = 0; j < n_q; ++j) {
+            mbar_wait(bar(kBarDqFull), s & 1, &abort_flag, p.status);
+            tc_fence_after();
+            if (lane == 0) bulk_wait_group_read0();  // the previous reductions have read the staging rows
+            __syncwarp();
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+              uint32_t r[32];
+              tmem_ld32(tm_dq + lane_off + 32 * half, r);
+              tmem_wait_ld();
+              if (half == 1) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(kBarDqFree));  // the dQ tile is out of tensor memory
+              }
+#pragma unroll
+              for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(stage + half * kTileBytes + swz128(lane, c)) =
+                    make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_reduce_add_3d(&tmap_dq, smem_u32(stage), 0, row, h);
+              tma_reduce_add_3d(&tmap_dq, smem_u32(stage + kTileBytes), 32, row, h);
+              bulk_commit_group();
+            }
+            ++s;
+            row += kTile;
+            if (row == row_end) row -= n_q * kTile;
           }
         }
-        if (j >= kBwdStages && lane == 0)
-          mbar_wait(bar(kBarQdoEmpty + qs), ((j / kBwdStages) - 1) & 1, &abort_flag, p.status);
-        __syncwarp();
-        if (lane == 0 && j > 0) {  // tile 0 is already on its way
-          mbar_arrive_expect_tx(bar(kBarQdoFull + qs), 2 * kTileBytes);
-          tma_load_4d(sQ(qs), &tmap_q, bar(kBarQdoFull + qs), 0, q_begin + jt * kTile, h, bcoord);
-          tma_load_4d(sDO(qs), &tmap_do, bar(kBarQdoFull + qs), 0, q_begin + jt * kTile, h, bcoord);
-        }
+      }
+      // dV and dK leave through this warp as well; the item is read again rather than kept in
+      // registers across the step loop.
+      const BwdWork wk = bwd_work(p, round);
+      const int row0 = wk.kt * kTile + quad * 32;  // first key row of this warp within the sequence
+      const int64_t out_row = int64_t(wk.k_begin + row0);
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {  // 0: dV, 1: dK (scaled)
+        __nv_bfloat16* out = which == 0
+                                 ? p.dv + int64_t(wk.bcoord) * p.dv_sb + int64_t(wk.h) * p.dv_sh + out_row * p.dv_st
+                                 : p.dk + int64_t(wk.bcoord) * p.dk_sb + int64_t(wk.h) * p.dk_sh + out_row * p.dk_st;
+        const int64_t out_st = which == 0 ? p.dv_st : p.dk_st;
+        if (n_q == 0) {
+          // No queries at all: dK = dV = 0.
+          if (row0 + lane < wk.lk) {
 #pragma unroll
-        for (int r4 = 0; r4 < 4; ++r4) {
-          sLse[qs * kTile + r4 * 32 + lane] = l2[r4];
-          sDelta[qs * kTile + r4 * 32 + lane] = dl[r4];
+            for (int c = 0; c < 8; ++c)
+              reinterpret_cast<uint4*>(out + int64_t(lane) * out_st)[c] = make_uint4(0, 0, 0, 0);
+          }
+          continue;
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(kBarQdoFull + qs));
-      }
-      }
-    } else if (warp >= 12) {
-      // ---------------- dQ drain warps: tensor memory -> staged fp32 rows -> TMA add-reduction ----------------
-      // Warp 12+q owns tensor-memory lane quadrant q. It stages its 32 rows (two 32-column halves,
-      // 128-byte swizzled rows) in shared memory and one lane issues the TMA add-reductions, so
-      // only warp-level synchronisation is needed and L2 receives whole 128-byte lines. Rows past
-      // the end of the sequence are staged as exact zeros, so adding them is harmless.
-      setmaxnreg_dec<kBwdDrainRegs>();
-      const int quad = warp & 3;
-      const uint32_t lane_off = uint32_t(quad * 32) << 16;
-      const int64_t acc_batch_row = int64_t(p.cu_q != nullptr ? 0 : b) * p.lq + q_begin;
-      uint8_t* stage = sDQ_ptr + quad * 4096;
-      for (int j = 0; j < n_q; ++j) {
-        const int tile = (j + kt) % n_q;
-        mbar_wait(bar(kBarDqFull), j & 1, &abort_flag, p.status);
+        mbar_wait(bar(which == 0 ? kBarDvDone : kBarDkDone), ni & 1, &abort_flag, p.status);
         tc_fence_after();
-        if (lane == 0) bulk_wait_group_read0();  // the previous reductions have read the staging rows
-        __syncwarp();
-#pragma unroll
+        const uint32_t tm_acc = (which == 0 ? tm_dv : tm_dk) + lane_off;
+        const float out_scale = which == 0 ? 1.f : p.scale;
+#pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t r[32];
-          tmem_ld32(tm_dq + lane_off + 32 * half, r);
+          tmem_ld32(tm_acc + 32 * half, r);
           tmem_wait_ld();
           if (half == 1) {
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(kBarDqFree));  // the dQ tile is out of tensor memory
+            if (lane == 0) mbar_arrive(bar(which == 0 ? kBarDvOut : kBarDkOut));  // the accumulator is free
           }
+          // Row `lane` of the scratch holds 32 bf16 = four 16-byte chunks, XOR-ed with the row pair's
+          // index so that neither the writes (a row per lane) nor the reads (four lanes per row)
+          // collide on banks.
 #pragma unroll
-          for (int c = 0; c < 8; ++c)
-            *reinterpret_cast<uint4*>(stage + half * kTileBytes + swz128(lane, c)) =
-                make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          const int row = int(acc_batch_row) + tile * kTile + quad * 32;
-          tma_reduce_add_3d(&tmap_dq, smem_u32(stage), 0, row, h);
-          tma_reduce_add_3d(&tmap_dq, smem_u32(stage + kTileBytes), 32, row, h);
-          bulk_commit_group();
+          for (int c = 0; c < 4; ++c) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r[8 * c + 0]) * out_scale, __uint_as_float(r[8 * c + 1]) * out_scale);
+            v.y = pack_bf16(__uint_as_float(r[8 * c + 2]) * out_scale, __uint_as_float(r[8 * c + 3]) * out_scale);
+            v.z = pack_bf16(__uint_as_float(r[8 * c + 4]) * out_scale, __uint_as_float(r[8 * c + 5]) * out_scale);
+            v.w = pack_bf16(__uint_as_float(r[8 * c + 6]) * out_scale, __uint_as_float(r[8 * c + 7]) * out_scale);
+            *reinterpret_cast<uint4*>(ostage + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) = v;
+          }
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int rloc = it * 8 + (lane >> 2), c = lane & 3;
+            const uint4 v = *reinterpret_cast<const uint4*>(ostage + rloc * 64 + ((c ^ ((rloc >> 1) & 3)) << 4));
+            if (row0 + rloc < wk.lk)
+              *reinterpret_cast<uint4*>(out + int64_t(rloc) * out_st + half * 32 + c * 8) = v;
+          }
+          __syncwarp();
         }
       }
-      if (lane == 0) bulk_wait_group_read0();  // the staging rows must outlive the TMA engine's reads
-    } else if (warp >= 8) {
-      setmaxnreg_dec<kBwdIssuerRegs>();
+      if (n_q > 0) ++ni;
+    }
+    if (lane == 0) bulk_wait_group_read0();  // the staging rows must outlive the TMA engine's reads
+  } else if (warp >= 8) {
+    setmaxnreg_dec<kBwdIssuerRegs>();
+    // Each issuer is one elected thread that walks the CTA's steps by their control words.
+    if (elect_one()) {
+      BwdStepPos pos;
+      uint32_t ni = 0;  // items started
+      volatile uint32_t* ctrl_ring = sCtrl;
       if (warp == 8) {
-      // ---------------- MMA issuer: S^T = K Q^T and dP^T = V dO^T ----------------
-      if (elect_one()) {
-        const uint64_t kd = make_sdesc(sK, 16, 1024), vd = make_sdesc(sV, 16, 1024);
-        mbar_wait(bar(kBarKvFull), 0, &abort_flag, p.status);
-        for (int j = 0; j < n_q; ++j) {
-          const int qs = j % kBwdStages;
-          mbar_wait(bar(kBarQdoFull + qs), (j / kBwdStages) & 1, &abort_flag, p.status);
-          if (j > 0) mbar_wait(bar(kBarSFree), (j - 1) & 1, &abort_flag, p.status);
+        // ---------------- MMA issuer: S^T = K Q^T and dP^T = V dO^T ----------------
+        const uint64_t vd = make_sdesc(sV, 16, 1024);
+        uint64_t kd = 0;
+#pragma unroll 1
+        for (;; pos.advance()) {
+          if (!mbar_wait(bar(kBarQdoFull + pos.qs), pos.qph, &abort_flag, p.status)) break;
+          const uint32_t ctrl = ctrl_ring[pos.qs];
+          if (ctrl & kCtrlStop) {
+            // The compute warps wait for the stage and for S^T together, so the stop mark needs an
+            // arrival on the S^T barrier -- once they have consumed the previous step's phase (a
+            // barrier must never run two phases ahead of a waiter that tests by parity).
+            if (pos.s > 0) mbar_wait(bar(kBarSFree), (pos.s - 1) & 1, &abort_flag, p.status);
+            mbar_arrive(bar(kBarSFull));
+            break;
+          }
+          if (ctrl & kCtrlFirst) {
+            const uint32_t kb = (ctrl & kCtrlKb) ? 1u : 0u;
+            kd = make_sdesc(sK(kb), 16, 1024);
+            mbar_wait(bar(kBarKFull + kb), (ni >> 1) & 1, &abort_flag, p.status);
+          }
+          if (pos.s > 0) mbar_wait(bar(kBarSFree), (pos.s - 1) & 1, &abort_flag, p.status);
           tc_fence_after();
-          const uint64_t qd = make_sdesc(sQ(qs), 16, 1024), gd = make_sdesc(sDO(qs), 16, 1024);
-#pragma unroll
+          const uint64_t qd = make_sdesc(sQ(pos.qs), 16, 1024), gd = make_sdesc(sDO(pos.qs), 16, 1024);
+#pragma unroll 1
           for (int k = 0; k < 4; ++k) mma_ss(tm_s, kd + 2 * k, qd + 2 * k, kIdescS, k > 0);
           tc_commit(bar(kBarSFull));
-          if (j > 0) mbar_wait(bar(kBarDpFree), (j - 1) & 1, &abort_flag, p.status);
+          if (ctrl & kCtrlFirst) mbar_wait(bar(kBarVFull), ni & 1, &abort_flag, p.status);
+          if (pos.s > 0) mbar_wait(bar(kBarDpFree), (pos.s - 1) & 1, &abort_flag, p.status);
           tc_fence_after();
-#pragma unroll
+#pragma unroll 1
           for (int k = 0; k < 4; ++k) mma_ss(tm_dp, vd + 2 * k, gd + 2 * k, kIdescS, k > 0);
           tc_commit(bar(kBarDpFull));
-          tc_commit(bar(kBarQdoEmpty + qs));
+          tc_commit(bar(kBarQdoEmpty + pos.qs));
+          if (ctrl & kCtrlLast) {
+            tc_commit(bar(kBarVFree));
+            ++ni;
+          }
         }
-      }
       } else if (warp == 9) {
-      // ---------------- MMA issuer: dV += P^T dO ----------------
-      if (elect_one()) {
-        for (int j = 0; j < n_q; ++j) {
-          const int qs = j % kBwdStages;
-          mbar_wait(bar(kBarPFull), j & 1, &abort_flag, p.status);
-          mbar_wait(bar(kBarQdoFull + qs), (j / kBwdStages) & 1, &abort_flag, p.status);
+        // ---------------- MMA issuer: dV += P^T dO ----------------
+#pragma unroll 1
+        for (;; pos.advance()) {
+          if (!mbar_wait(bar(kBarQdoFull + pos.qs), pos.qph, &abort_flag, p.status)) break;
+          const uint32_t ctrl = ctrl_ring[pos.qs];
+          if (ctrl & kCtrlStop) break;
+          const bool first = (ctrl & kCtrlFirst) != 0;
+          // The previous item's dV has to be out of tensor memory before this one's first MMA.
+          if (first && ni > 0) mbar_wait(bar(kBarDvOut), (ni - 1) & 1, &abort_flag, p.status);
+          mbar_wait(bar(kBarPFull), pos.s & 1, &abort_flag, p.status);
           tc_fence_after();
-          const uint64_t gd_mn = make_sdesc(sDO(qs), 1024, 1024);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) mma_ts(tm_dv, tm_pt + 8 * k, gd_mn + 128 * k, kIdescKN, (j > 0) || (k > 0));
+          const uint64_t gd_mn = make_sdesc(sDO(pos.qs), 1024, 1024);
+#pragma unroll 1
+          for (int k = 0; k < 8; ++k) mma_ts(tm_dv, tm_pt + 8 * k, gd_mn + 128 * k, kIdescKN, !first || (k > 0));
           tc_commit(bar(kBarPtFree));
-          tc_commit(bar(kBarQdoEmpty + qs));
+          tc_commit(bar(kBarQdoEmpty + pos.qs));
+          if (ctrl & kCtrlLast) {
+            tc_commit(bar(kBarDvDone));
+            ++ni;
+          }
         }
-      }
       } else if (warp == 10) {
-      // ---------------- MMA issuer: dK += dS^T Q ----------------
-      if (elect_one()) {
-        for (int j = 0; j < n_q; ++j) {
-          const int qs = j % kBwdStages;
-          mbar_wait(bar(kBarDsFull), j & 1, &abort_flag, p.status);
-          mbar_wait(bar(kBarQdoFull + qs), (j / kBwdStages) & 1, &abort_flag, p.status);
+        // ---------------- MMA issuer: dK += dS^T Q ----------------
+#pragma unroll 1
+        for (;; pos.advance()) {
+          if (!mbar_wait(bar(kBarQdoFull + pos.qs), pos.qph, &abort_flag, p.status)) break;
+          const uint32_t ctrl = ctrl_ring[pos.qs];
+          if (ctrl & kCtrlStop) break;
+          const bool first = (ctrl & kCtrlFirst) != 0;
+          if (first && ni > 0) mbar_wait(bar(kBarDkOut), (ni - 1) & 1, &abort_flag, p.status);
+          mbar_wait(bar(kBarDsFull), pos.s & 1, &abort_flag, p.status);
           tc_fence_after();
-          const uint64_t qd_mn = make_sdesc(sQ(qs), 1024, 1024);
-#pragma unroll
+          const uint64_t qd_mn = make_sdesc(sQ(pos.qs), 1024, 1024);
+#pragma unroll 1
           for (int k = 0; k < 8; ++k) {
             // A: K-major view of the dS buffer; one K step = 16 query columns.
             const uint64_t ad = make_sdesc(sDS + (k >> 2) * kTileBytes, 16, 1024) + 2 * (k & 3);
-            mma_ss(tm_dk, ad, qd_mn + 128 * k, kIdescKN, (j > 0) || (k > 0));
+            mma_ss(tm_dk, ad, qd_mn + 128 * k, kIdescKN, !first || (k > 0));
           }
           tc_commit(bar(kBarDsFree));
-          tc_commit(bar(kBarQdoEmpty + qs));
+          tc_commit(bar(kBarQdoEmpty + pos.qs));
+          if (ctrl & kCtrlLast) {
+            tc_commit(bar(kBarDkDone));
+            ++ni;
+          }
         }
-        tc_commit(bar(kBarDkDone));
-      }
       } else {
-      // ---------------- MMA issuer: dQ = dS K ----------------
-      if (elect_one()) {
-        const uint64_t kd_mn = make_sdesc(sK, 1024, 1024);
-        mbar_wait(bar(kBarKvFull), 0, &abort_flag, p.status);
-        for (int j = 0; j < n_q; ++j) {
-          mbar_wait(bar(kBarDsFull), j & 1, &abort_flag, p.status);
-          if (j > 0) mbar_wait(bar(kBarDqFree), (j - 1) & 1, &abort_flag, p.status);
+        // ---------------- MMA issuer: dQ = dS K ----------------
+        // A: MN-major view of the same dS bytes; one K step = 16 key rows.
+        const uint64_t ds_mn = make_sdesc(sDS, kTileBytes, 1024);
+        uint64_t kd_mn = 0;
+        uint32_t kb = 0;
+#pragma unroll 1
+        for (;; pos.advance()) {
+          if (!mbar_wait(bar(kBarQdoFull + pos.qs), pos.qph, &abort_flag, p.status)) break;
+          // This issuer does not hold the stage (the path from a stage becoming free to becoming full
+          // again is the tightest in the pipeline), so it reads a copy that is overwritten four steps
+          // later: that write comes after the dK MMA of step s+1, which follows this step's dQ MMA.
+          const uint32_t ctrl = (reinterpret_cast<volatile uint32_t*>(sCtrlQ))[pos.s & 3u];
+          if (ctrl & kCtrlStop) break;
+          if (ctrl & kCtrlFirst) {
+            kb = (ctrl & kCtrlKb) ? 1u : 0u;
+            kd_mn = make_sdesc(sK(kb), 1024, 1024);
+            mbar_wait(bar(kBarKFull + kb), (ni >> 1) & 1, &abort_flag, p.status);
+          }
+          mbar_wait(bar(kBarDsFull), pos.s & 1, &abort_flag, p.status);
+          if (pos.s > 0) mbar_wait(bar(kBarDqFree), (pos.s - 1) & 1, &abort_flag, p.status);
           tc_fence_after();
-          // A: MN-major view of the same dS bytes; one K step = 16 key rows.
-          const uint64_t ds_mn = make_sdesc(sDS, kTileBytes, 1024);
-#pragma unroll
+#pragma unroll 1
           for (int k = 0; k < 8; ++k) mma_ss(tm_dq, ds_mn + 128 * k, kd_mn + 128 * k, kIdescNN, k > 0);
           tc_commit(bar(kBarDqFull));
           tc_commit(bar(kBarDsFree));
-        }
-      }
-      }
-    } else {
-      // ---------------- compute warpgroups: w = 0 / 1 owns query columns [64w, 64w+64) ----------------
-      setmaxnreg_inc<kBwdComputeRegs>();
-      const int w = warp >> 2;
-      const int krow_in_tile = tid & 127;  // key row of this thread = tensor-memory lane
-      const uint32_t lane_off = uint32_t((warp & 3) * 32) << 16;
-      const bool row_valid = (k_row0 + krow_in_tile) < lk;
-      const bool partial = (k_row0 + kTile) > lk;
-      const uint64_t scale2 = pack_f32x2(p.scale_log2, p.scale_log2);
-      // Iteration that visits the last, ragged query tile (-1 if the length is a multiple of the tile).
-      const int j_ragged = (lq % kTile) != 0 ? (n_q - 1 - kt % n_q + n_q) % n_q : -1;
-      for (int j = 0; j < n_q; ++j) {
-        const int qs = j % kBwdStages;
-        const float4* lse4 = reinterpret_cast<const float4*>(sLse + qs * kTile + 64 * w);   // -lse (log2)
-        const float4* dl4 = reinterpret_cast<const float4*>(sDelta + qs * kTile + 64 * w);  // -delta
-        uint64_t pf[32];  // P^T values of this thread as packed fp32 pairs
-
-        bool pt_ok, dp_ok;
-        // ---- phase A: P^T = exp2(S^T * scale_log2 - lse) ----
-        mbar_wait2(bar(kBarQdoFull + qs), (j / kBwdStages) & 1, bar(kBarSFull), j & 1, &abort_flag, p.status);
-        tc_fence_after();
-        {
-          uint32_t ra[32], rb[32];
-          tmem_ld32(tm_s + lane_off + 64 * w, ra);
-          tmem_ld32(tm_s + lane_off + 64 * w + 32, rb);
-          tmem_wait_ld();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(kBarSFree));
-          // Poll the barriers needed after the exponentials now; the polls' latency overlaps them.
-          pt_ok = j > 0 ? mbar_try_wait(bar(kBarPtFree), (j - 1) & 1) : true;
-          dp_ok = mbar_try_wait(bar(kBarDpFull), j & 1);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const uint32_t* src = i < 8 ? &ra[4 * i] : &rb[4 * (i - 8)];
-            const float4 l = lse4[i];
-            float x0, x1, x2, x3;
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(src[0]), __uint_as_float(src[1])), scale2,
-                                   pack_f32x2(l.x, l.y)), x0, x1);
-            unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(src[2]), __uint_as_float(src[3])), scale2,
-                                   pack_f32x2(l.z, l.w)), x2, x3);
-            pf[2 * i] = pack_f32x2(fast_exp2(x0), fast_exp2(x1));
-            // Every other second pair goes to the FMA pipe: the exponentials are this phase's
-            // bottleneck (both warps of an SM sub-partition run it together on one MUFU unit).
-            if (i & 1) pf[2 * i + 1] = exp2_poly_f32x2(pack_f32x2(x2, x3));
-            else pf[2 * i + 1] = pack_f32x2(fast_exp2(x2), fast_exp2(x3));
+          if (ctrl & kCtrlLast) {
+            tc_commit(bar(kBarKFree + kb));
+            ++ni;
           }
         }
-        if (partial && !row_valid) {
-          // Key rows past the end of the sequence must not contribute to dQ.
-#pragma unroll
-          for (int i = 0; i < 32; ++i) pf[i] = 0ull;
-        }
-        if (j == j_ragged) {
-          // Query columns past the end of the sequence: the hardware exponential already gave 0 for
-          // their -inf argument, the polynomial's clamp gave 2^-126. Make all of them exactly 0, so
-          // that nothing at all is added to the dQ rows of the next packed sequence.
-          const int valid = lq - (n_q - 1) * kTile - 64 * w;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float a0, a1;
-            unpack_f32x2(pf[i], a0, a1);
-            pf[i] = pack_f32x2(2 * i < valid ? a0 : 0.f, 2 * i + 1 < valid ? a1 : 0.f);
-          }
-        }
-        if (j > 0) {
-          if (!pt_ok) mbar_wait(bar(kBarPtFree), (j - 1) & 1, &abort_flag, p.status);
-          tc_fence_after();
-        }
-        {
-          uint32_t pk[16];
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              float a0, a1;
-              unpack_f32x2(pf[16 * c + i], a0, a1);
-              pk[i] = pack_bf16(a0, a1);
-            }
-            tmem_st16(tm_pt + lane_off + 32 * w + 16 * c, pk);
-          }
-        }
-
-        // ---- middle: pull dP^T of this tile out of tensor memory ----
-        uint32_t ra[32], rb[32];
-        if (!dp_ok) mbar_wait(bar(kBarDpFull), j & 1, &abort_flag, p.status);
-        tc_fence_after();
-        const bool ds_ok = j > 0 ? mbar_try_wait(bar(kBarDsFree), (j - 1) & 1) : true;
-        tmem_ld32(tm_dp + lane_off + 64 * w, ra);
-        tmem_ld32(tm_dp + lane_off + 64 * w + 32, rb);
-        tmem_wait_ld();
-        tmem_wait_st();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bar(kBarPFull));
-          mbar_arrive(bar(kBarDpFree));
-        }
-
-        // ---- phase B: dS^T = P^T o (dP^T - delta) -> shared memory ----
-        if (!ds_ok) mbar_wait(bar(kBarDsFree), (j - 1) & 1, &abort_flag, p.status);
-        uint8_t* half = sDS_ptr + w * kTileBytes;
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {  // 16-byte chunk c = query columns [8c, 8c+8) of this half
-          const uint32_t* src = c < 4 ? &ra[8 * c] : &rb[8 * (c - 4)];
-          const float4 d0 = dl4[2 * c], d1 = dl4[2 * c + 1];
-          const uint64_t nd[4] = {pack_f32x2(d0.x, d0.y), pack_f32x2(d0.z, d0.w), pack_f32x2(d1.x, d1.y),
-                                  pack_f32x2(d1.z, d1.w)};
-          uint32_t o[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint64_t dp2 = pack_f32x2(__uint_as_float(src[2 * i]), __uint_as_float(src[2 * i + 1]));
-            float a0, a1;
-            unpack_f32x2(mul_f32x2(pf[4 * c + i], add_f32x2(dp2, nd[i])), a0, a1);
-            o[i] = pack_bf16(a0, a1);
-          }
-          *reinterpret_cast<uint4*>(half + swz128(krow_in_tile, c)) = make_uint4(o[0], o[1], o[2], o[3]);
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(kBarDsFull));
-      }
-      // ---- epilogue: warpgroup 0 stores dV, warpgroup 1 stores dK (scaled) ----
-      // Warpgroup 0 needs dV complete (the last P^T consumed), warpgroup 1 needs dK complete.
-      if (w == 0) mbar_wait(bar(kBarPtFree), (n_q - 1) & 1, &abort_flag, p.status);
-      else mbar_wait(bar(kBarDkDone), 0, &abort_flag, p.status);
-      tc_fence_after();
-      // Each warp turns its 32 accumulator rows into bf16 in a 4 KB scratch area and writes them out
-      // with eight lanes per 128-byte row, so the stores are whole lines. Only warp-level
-      // synchronisation is needed: a warp reads back what it wrote. The scratch is dead operand
-      // space: warpgroup 0 uses the V tile (last read by the final dP^T MMA, long complete when the
-      // final dV MMA is), warpgroup 1 the first Q stage (read only by S^T and dK MMAs, all complete).
-      uint8_t* scratch = smem_al + (1 + w) * kTileBytes + (warp & 3) * 4096;
-      const float out_scale = w == 0 ? 1.f : p.scale;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32((w == 0 ? tm_dv : tm_dk) + lane_off + c * 32, r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint4 v;
-          v.x = pack_bf16(__uint_as_float(r[8 * i + 0]) * out_scale, __uint_as_float(r[8 * i + 1]) * out_scale);
-          v.y = pack_bf16(__uint_as_float(r[8 * i + 2]) * out_scale, __uint_as_float(r[8 * i + 3]) * out_scale);
-          v.z = pack_bf16(__uint_as_float(r[8 * i + 4]) * out_scale, __uint_as_float(r[8 * i + 5]) * out_scale);
-          v.w = pack_bf16(__uint_as_float(r[8 * i + 6]) * out_scale, __uint_as_float(r[8 * i + 7]) * out_scale);
-          *reinterpret_cast<uint4*>(scratch + swz128(lane, c * 4 + i)) = v;
-        }
-      }
-      __syncwarp();
-      __nv_bfloat16* out_base = w == 0 ? p.dv + int64_t(bcoord) * p.dv_sb + int64_t(h) * p.dv_sh
-                                       : p.dk + int64_t(bcoord) * p.dk_sb + int64_t(h) * p.dk_sh;
-      const int64_t out_st = w == 0 ? p.dv_st : p.dk_st;
-#pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int rloc = it * 4 + (lane >> 3);
-        const int krow = k_row0 + (warp & 3) * 32 + rloc;
-        const uint4 v = *reinterpret_cast<const uint4*>(scratch + swz128(rloc, lane & 7));
-        if (krow < lk) *reinterpret_cast<uint4*>(out_base + int64_t(k_begin + krow) * out_st + (lane & 7) * 8) = v;
       }
     }
-  } else if (warp < 8) {
-    // No queries at all: dK = dV = 0.
-    const int w = warp >> 2;
-    const int krow = k_row0 + (tid & 127);
-    if (krow < lk) {
-      __nv_bfloat16* out_ptr =
-          w == 0 ? p.dv + int64_t(bcoord) * p.dv_sb + int64_t(k_begin + krow) * p.dv_st + int64_t(h) * p.dv_sh
-                 : p.dk + int64_t(bcoord) * p.dk_sb + int64_t(k_begin + krow) * p.dk_st + int64_t(h) * p.dk_sh;
-      for (int c = 0; c < 8; ++c) reinterpret_cast<uint4*>(out_ptr)[c] = make_uint4(0, 0, 0, 0);
-    }
+  } else {
+    // ---------------- compute warpgroups: w = 0 / 1 owns query columns [64w, 64w+64) ----------------
+    setmaxnreg_inc<kBwdComputeRegs>();
+    bwd_compute_role(bar0, &abort_flag, p.status, tmem_base, sLse, sDelta, sCtrl, sDS_ptr, p.scale_log2);
   }
 
   tc_fence_before();

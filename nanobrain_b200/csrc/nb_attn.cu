@@ -46,6 +46,7 @@ EncodeTiledFn get_encode() {
 constexpr int kMaxDevices = 64;
 std::mutex g_dev_mutex;
 int g_dev_state[kMaxDevices];  // 0 = not set up, 1 = ready, <0 = error code (negated)
+int g_dev_sms[kMaxDevices];    // SM count, valid once the device is ready
 
 // Once per device: check the architecture and opt the kernels into their dynamic shared memory.
 int ensure_device_ready() {
@@ -57,7 +58,9 @@ int ensure_device_ready() {
   if (g_dev_state[dev] < 0) return -g_dev_state[dev];
   int major = 0;
   int rc = NB_ATTN_OK;
-  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&g_dev_sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      g_dev_sms[dev] <= 0) {
     rc = NB_ATTN_ERR_LAUNCH;
   } else if (major != 10) {
     rc = NB_ATTN_ERR_DEVICE;
@@ -71,6 +74,14 @@ int ensure_device_ready() {
   }
   g_dev_state[dev] = rc == NB_ATTN_OK ? 1 : -rc;
   return rc;
+}
+
+// SM count of the current device (after ensure_device_ready succeeded on it).
+int device_sm_count() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 1;
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  return g_dev_sms[dev] > 0 ? g_dev_sms[dev] : 1;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -93,6 +104,8 @@ int check_shape(const nb_attn_shape& s) {
   if (s.cu_seqlens_q == nullptr) {
     if (s.total_q != int64_t(s.batch) * s.max_seqlen_q || s.total_k != int64_t(s.batch) * s.max_seqlen_k)
       return NB_ATTN_ERR_SHAPE;
+    // The backward kernel counts its work units (key tiles x heads x sequences) in 32 bits.
+    if ((int64_t(s.max_seqlen_k) + nb::kTile - 1) / nb::kTile * s.heads * s.batch > INT32_MAX) return NB_ATTN_ERR_SHAPE;
   } else {
     if (s.total_q > INT32_MAX || s.total_k > INT32_MAX) return NB_ATTN_ERR_SHAPE;
     // The grid is items x heads.
@@ -267,10 +280,14 @@ int launch_bwd(const nb_attn_bwd_args* a, void* workspace, size_t workspace_byte
   p.scale = s.scale;
   p.scale_log2 = s.scale * kLog2e;
   p.status = a->status;
-  dim3 grid(ceil_div(s.max_seqlen_k, nb::kTile), s.heads, s.batch);
+  // The main kernel's CTAs are persistent: one per SM, each walking its share of the work units
+  // (key tiles x heads x sequences, or work-list entries x heads).
+  int64_t n_work = 0;
+  p.n_kt = ceil_div(s.max_seqlen_k, nb::kTile);
   if (dense) {
     p.items = nullptr;
     p.sched = nb::SchedParams{};
+    n_work = int64_t(p.n_kt) * s.heads * s.batch;
   } else {
     // Block 0 of the prologue builds the list of key tiles; the main kernel runs items x heads CTAs.
     const int64_t n_items = nb::sched_capacity(s.total_k, s.batch);
@@ -278,8 +295,13 @@ int launch_bwd(const nb_attn_bwd_args* a, void* workspace, size_t workspace_byte
         reinterpret_cast<nb::SchedItem*>(static_cast<unsigned char*>(workspace) + bwd_items_offset(s));
     p.items = items;
     p.sched = make_sched(s, 1, items, n_items, a->status);
-    grid = dim3(unsigned(n_items * s.heads), 1, 1);
+    n_work = n_items * s.heads;
   }
+  p.n_work = int32_t(n_work);
+  p.div_heads = nb::make_fast_div(uint32_t(s.heads));
+  p.div_n_kt = nb::make_fast_div(uint32_t(p.n_kt));
+  const int sms = device_sm_count();
+  const dim3 grid(unsigned(n_work < sms ? n_work : sms), 1, 1);
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t rows = s.total_q * s.heads;

@@ -98,25 +98,37 @@ enum : int { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadSeqlens = 2 };
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // about two seconds
 
 // Bounded wait. `abort_flag` lives in shared memory and is shared by the whole CTA. The attention
-// kernels use the default limit (a compile-time constant); the wait self-test passes its own.
+// kernels use the default limit (a compile-time constant); the wait self-test passes its own
+// (at most 4 s: the clock is the low word of the nanosecond timer).
+// The loop is kept as small as it can be -- 32-bit timer arithmetic, the flag and the status word
+// touched with plain state-space stores: the warp-specialised kernels have dozens of wait sites,
+// every one of them inlined, and their hot code has to fit the SM's instruction cache (with a
+// larger loop the backward kernel's instruction-cache hit rate was 92 % at best and instruction
+// fetch was its top stall).
+__device__ __forceinline__ uint32_t globaltimer_lo() {
+  uint32_t t;
+  asm volatile("mov.u32 %0, %%globaltimer_lo;" : "=r"(t));
+  return t;
+}
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status_word, uint64_t limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
-  uint64_t t0 = 0;
-  for (uint32_t it = 1;; ++it) {
+  const uint32_t flag_addr = smem_u32(const_cast<int*>(abort_flag));
+  const uint32_t limit = uint32_t(limit_ns);
+  const uint32_t t0 = globaltimer_lo();
+#pragma unroll 1
+  for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 0x3F) == 0) {
-      if (*abort_flag) return false;
-      uint64_t now = globaltimer_ns();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > limit_ns) {
-        *abort_flag = 1;
-        if (status_word) atomicExch(status_word, (int)kStatusWaitTimeout);
-        return false;
-      }
-    }
+    uint32_t flag;
+    asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(flag) : "r"(flag_addr) : "memory");
+    if (flag) return false;
+    if (globaltimer_lo() - t0 > limit) break;
   }
+  asm volatile("st.volatile.shared.u32 [%0], %1;" ::"r"(flag_addr), "r"(1) : "memory");
+  if (status_word)
+    asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(status_word), "r"((int)kStatusWaitTimeout) : "memory");
+  return false;
 }
 
 // ----------------------------------------------------------------------------------------
