@@ -603,14 +603,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       }
     }
   } else if (warp >= 12) {
-    // ---------------- drain warps: dQ tiles every step, dV and dK at the end of an item ----------------
+    // ---------------- drain warps: dQ tiles every step, dV and dK once per item ----------------
     // Warp 12+q owns tensor-memory lane quadrant q. dQ: it stages its 32 rows (two 32-column
     // halves, 128-byte swizzled rows) in shared memory and one lane issues the TMA add-reductions,
     // so only warp-level synchronisation is needed and L2 receives whole 128-byte lines. Rows past
     // the end of the sequence are staged as exact zeros, so adding them is harmless. dV / dK: when
     // the item's last MMA into the accumulator is complete the warp turns its 32 rows into bf16,
     // 32 columns at a time through a 2 KB scratch area, and stores them four lanes per 64-byte
-    // half row; the issuers start the next item's first dV / dK MMA only after that.
+    // half row; the issuers start the next item's first dV / dK MMA only after the accumulator has
+    // been read. dV is complete half a step before the item's last dQ tile, so it is taken out
+    // before that tile is drained; dK follows the tile. (With both after it, every item's second
+    // step waited ~2900 cycles for the next dV / dK MMA.)
     setmaxnreg_dec<kBwdDrainRegs>();
     const int quad = warp & 3;
     const uint32_t lane_off = uint32_t(quad * 32) << 16;
@@ -619,108 +622,102 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     uint32_t s = 0, ni = 0;
 #pragma unroll 1
     for (uint32_t round = 0;; ++round) {
-      int n_q;
-      {
-        // The step loop keeps only what it needs of the work item (this role has 56 registers).
-        const BwdWork wk = bwd_work(p, round);
-        n_q = wk.n_q;
-        if (n_q < 0) break;
-        if (n_q > 0) {
-          const int h = wk.h;
-          int row = (packed ? 0 : wk.b * p.lq) + wk.q_begin + quad * 32 + bwd_first_tile(wk.kt, n_q) * kTile;
-          const int row_end = (packed ? 0 : wk.b * p.lq) + wk.q_begin + quad * 32 + n_q * kTile;
-#pragma unroll 1
-          for (int j = 0; j < n_q; ++j) {
-            mbar_wait(bar(kBarDqFull), s & 1, &abort_flag, p.status);
-            tc_fence_after();
-            if (lane == 0) bulk_wait_group_read0();  // the previous reductions have read the staging rows
-            __syncwarp();
-#pragma unroll 1
-            for (int half = 0; half < 2; ++half) {
-              uint32_t r[32];
-              tmem_ld32(tm_dq + lane_off + 32 * half, r);
-              tmem_wait_ld();
-              if (half == 1) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar(kBarDqFree));  // the dQ tile is out of tensor memory
-              }
+      const BwdWork wk = bwd_work(p, round);
+      const int n_q = wk.n_q;
+      if (n_q < 0) break;
+      const int h = wk.h;
+      const int rows_live = wk.lk - wk.kt * kTile - quad * 32;  // this warp's rows below that exist
+      const int64_t out_row = int64_t(wk.k_begin + wk.kt * kTile + quad * 32);
+      const int64_t dv_off = int64_t(wk.bcoord) * p.dv_sb + int64_t(h) * p.dv_sh + out_row * p.dv_st;
+      const int64_t dk_off = int64_t(wk.bcoord) * p.dk_sb + int64_t(h) * p.dk_sh + out_row * p.dk_st;
+      if (n_q == 0) {
+        // No queries at all: dK = dV = 0.
+        if (lane < rows_live) {
 #pragma unroll
-              for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(stage + half * kTileBytes + swz128(lane, c)) =
-                    make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_reduce_add_3d(&tmap_dq, smem_u32(stage), 0, row, h);
-              tma_reduce_add_3d(&tmap_dq, smem_u32(stage + kTileBytes), 32, row, h);
-              bulk_commit_group();
-            }
-            ++s;
-            row += kTile;
-            if (row == row_end) row -= n_q * kTile;
+          for (int c = 0; c < 8; ++c) {
+            reinterpret_cast<uint4*>(p.dv + dv_off + int64_t(lane) * p.dv_st)[c] = make_uint4(0, 0, 0, 0);
+            reinterpret_cast<uint4*>(p.dk + dk_off + int64_t(lane) * p.dk_st)[c] = make_uint4(0, 0, 0, 0);
           }
         }
+        continue;
       }
-      // dV and dK leave through this warp as well; the item is read again rather than kept in
-      // registers across the step loop.
-      const BwdWork wk = bwd_work(p, round);
-      const int row0 = wk.kt * kTile + quad * 32;  // first key row of this warp within the sequence
-      const int64_t out_row = int64_t(wk.k_begin + row0);
+      int row = (packed ? 0 : wk.b * p.lq) + wk.q_begin + quad * 32 + bwd_first_tile(wk.kt, n_q) * kTile;
+      const int row_end = (packed ? 0 : wk.b * p.lq) + wk.q_begin + quad * 32 + n_q * kTile;
+      // Events of an item, in order: the dQ tiles of steps 0 .. n_q-2, dV, the last dQ tile, dK.
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {  // 0: dV, 1: dK (scaled)
-        __nv_bfloat16* out = which == 0
-                                 ? p.dv + int64_t(wk.bcoord) * p.dv_sb + int64_t(wk.h) * p.dv_sh + out_row * p.dv_st
-                                 : p.dk + int64_t(wk.bcoord) * p.dk_sb + int64_t(wk.h) * p.dk_sh + out_row * p.dk_st;
-        const int64_t out_st = which == 0 ? p.dv_st : p.dk_st;
-        if (n_q == 0) {
-          // No queries at all: dK = dV = 0.
-          if (row0 + lane < wk.lk) {
+      for (int e = 0; e < n_q + 2; ++e) {
+        if (e == n_q - 1 || e == n_q + 1) {
+          const bool is_dk = e > n_q;
+          mbar_wait(bar(is_dk ? kBarDkDone : kBarDvDone), ni & 1, &abort_flag, p.status);
+          tc_fence_after();
+          const uint32_t tm_acc = (is_dk ? tm_dk : tm_dv) + lane_off;
+          const float out_scale = is_dk ? p.scale : 1.f;
+          __nv_bfloat16* out = is_dk ? p.dk + dk_off : p.dv + dv_off;
+          const int64_t out_st = is_dk ? p.dk_st : p.dv_st;
+#pragma unroll 1
+          for (int half = 0; half < 2; ++half) {
+            uint32_t r[32];
+            tmem_ld32(tm_acc + 32 * half, r);
+            tmem_wait_ld();
+            if (half == 1) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar(is_dk ? kBarDkOut : kBarDvOut));  // the accumulator is free
+            }
+            // Row `lane` of the scratch holds 32 bf16 = four 16-byte chunks, XOR-ed with the row
+            // pair's index so that neither the writes (a row per lane) nor the reads (four lanes per
+            // row) collide on banks.
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-              reinterpret_cast<uint4*>(out + int64_t(lane) * out_st)[c] = make_uint4(0, 0, 0, 0);
+            for (int c = 0; c < 4; ++c) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(r[8 * c + 0]) * out_scale, __uint_as_float(r[8 * c + 1]) * out_scale);
+              v.y = pack_bf16(__uint_as_float(r[8 * c + 2]) * out_scale, __uint_as_float(r[8 * c + 3]) * out_scale);
+              v.z = pack_bf16(__uint_as_float(r[8 * c + 4]) * out_scale, __uint_as_float(r[8 * c + 5]) * out_scale);
+              v.w = pack_bf16(__uint_as_float(r[8 * c + 6]) * out_scale, __uint_as_float(r[8 * c + 7]) * out_scale);
+              *reinterpret_cast<uint4*>(ostage + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) = v;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int it = 0; it < 4; ++it) {
+              const int rloc = it * 8 + (lane >> 2), c = lane & 3;
+              const uint4 v = *reinterpret_cast<const uint4*>(ostage + rloc * 64 + ((c ^ ((rloc >> 1) & 3)) << 4));
+              if (rloc < rows_live) *reinterpret_cast<uint4*>(out + int64_t(rloc) * out_st + half * 32 + c * 8) = v;
+            }
+            __syncwarp();
           }
           continue;
         }
-        mbar_wait(bar(which == 0 ? kBarDvDone : kBarDkDone), ni & 1, &abort_flag, p.status);
+        mbar_wait(bar(kBarDqFull), s & 1, &abort_flag, p.status);
         tc_fence_after();
-        const uint32_t tm_acc = (which == 0 ? tm_dv : tm_dk) + lane_off;
-        const float out_scale = which == 0 ? 1.f : p.scale;
+        if (lane == 0) bulk_wait_group_read0();  // the previous reductions have read the staging rows
+        __syncwarp();
 #pragma unroll 1
         for (int half = 0; half < 2; ++half) {
           uint32_t r[32];
-          tmem_ld32(tm_acc + 32 * half, r);
+          tmem_ld32(tm_dq + lane_off + 32 * half, r);
           tmem_wait_ld();
           if (half == 1) {
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar(which == 0 ? kBarDvOut : kBarDkOut));  // the accumulator is free
+            if (lane == 0) mbar_arrive(bar(kBarDqFree));  // the dQ tile is out of tensor memory
           }
-          // Row `lane` of the scratch holds 32 bf16 = four 16-byte chunks, XOR-ed with the row pair's
-          // index so that neither the writes (a row per lane) nor the reads (four lanes per row)
-          // collide on banks.
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(r[8 * c + 0]) * out_scale, __uint_as_float(r[8 * c + 1]) * out_scale);
-            v.y = pack_bf16(__uint_as_float(r[8 * c + 2]) * out_scale, __uint_as_float(r[8 * c + 3]) * out_scale);
-            v.z = pack_bf16(__uint_as_float(r[8 * c + 4]) * out_scale, __uint_as_float(r[8 * c + 5]) * out_scale);
-            v.w = pack_bf16(__uint_as_float(r[8 * c + 6]) * out_scale, __uint_as_float(r[8 * c + 7]) * out_scale);
-            *reinterpret_cast<uint4*>(ostage + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) = v;
-          }
-          __syncwarp();
-#pragma unroll
-          for (int it = 0; it < 4; ++it) {
-            const int rloc = it * 8 + (lane >> 2), c = lane & 3;
-            const uint4 v = *reinterpret_cast<const uint4*>(ostage + rloc * 64 + ((c ^ ((rloc >> 1) & 3)) << 4));
-            if (row0 + rloc < wk.lk)
-              *reinterpret_cast<uint4*>(out + int64_t(rloc) * out_st + half * 32 + c * 8) = v;
-          }
-          __syncwarp();
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(stage + half * kTileBytes + swz128(lane, c)) =
+                make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
         }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_3d(&tmap_dq, smem_u32(stage), 0, row, h);
+          tma_reduce_add_3d(&tmap_dq, smem_u32(stage + kTileBytes), 32, row, h);
+          bulk_commit_group();
+        }
+        ++s;
+        row += kTile;
+        if (row == row_end) row -= n_q * kTile;
       }
-      if (n_q > 0) ++ni;
+      ++ni;
     }
     if (lane == 0) bulk_wait_group_read0();  // the staging rows must outlive the TMA engine's reads
   } else if (warp >= 8) {
