@@ -78,6 +78,10 @@ inline FastDiv make_fast_div(uint32_t d) {
   return f;
 }
 
+#ifndef NB_BWD_L2_HINTS
+#define NB_BWD_L2_HINTS 1
+#endif
+
 struct BwdParams {
   const __nv_bfloat16 *o, *d_o;
   int64_t o_sb, o_st, o_sh, do_sb, do_st, do_sh;
@@ -112,6 +116,9 @@ __global__ void __launch_bounds__(256) attn_bwd_prologue_kernel(const BwdParams 
   const int lane8 = threadIdx.x & 7;
   int64_t row = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
   const int64_t row_step = (int64_t(gridDim.x) * blockDim.x) >> 3;
+#if NB_BWD_L2_HINTS
+  const uint64_t keep = l2_policy_evict_last();
+#endif
   for (; row < n_rows; row += row_step) {
     const int64_t t = row / p.heads;
     const int h = int(row - t * p.heads);
@@ -142,8 +149,13 @@ __global__ void __launch_bounds__(256) attn_bwd_prologue_kernel(const BwdParams 
     if (lane8 == 0) p.delta[didx] = acc;
     float4* acc_row = reinterpret_cast<float4*>(p.dq_accum + row * kHeadDim);
     const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+#if NB_BWD_L2_HINTS
+    st_global_v4_hint(acc_row + lane8 * 2, z, keep);
+    st_global_v4_hint(acc_row + lane8 * 2 + 1, z, keep);
+#else
     acc_row[lane8 * 2] = z;
     acc_row[lane8 * 2 + 1] = z;
+#endif
   }
 }
 
@@ -153,6 +165,9 @@ __global__ void __launch_bounds__(256) attn_bwd_prologue_kernel(const BwdParams 
 __global__ void __launch_bounds__(256) attn_bwd_epilogue_kernel(const BwdParams p) {
   pdl_wait();  // the accumulator is complete when the main kernel is
   pdl_launch_dependents();
+#if NB_BWD_L2_HINTS
+  const uint64_t drop = l2_policy_evict_first();
+#endif
   const int64_t n_rows = p.total_q * p.heads;
   const int lane8 = threadIdx.x & 7;
   int64_t row = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
@@ -166,7 +181,11 @@ __global__ void __launch_bounds__(256) attn_bwd_epilogue_kernel(const BwdParams 
       tok = t - b * p.lq;
     }
     const float4* acc_row = reinterpret_cast<const float4*>(p.dq_accum + row * kHeadDim);
+#if NB_BWD_L2_HINTS
+    const float4 x = ld_global_v4_hint(acc_row + lane8 * 2, drop), y = ld_global_v4_hint(acc_row + lane8 * 2 + 1, drop);
+#else
     const float4 x = acc_row[lane8 * 2], y = acc_row[lane8 * 2 + 1];
+#endif
     uint4 v;
     v.x = pack_bf16(x.x * p.scale, x.y * p.scale);
     v.y = pack_bf16(x.z * p.scale, x.w * p.scale);
@@ -619,6 +638,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     uint8_t* stage = sDQ_ptr + quad * 4096;
     uint8_t* ostage = sOut_ptr + quad * (kBwdOutStageBytes / 4);
     uint32_t s = 0, ni = 0;
+#if NB_BWD_L2_HINTS
+    const uint64_t keep = l2_policy_evict_last();
+#endif
 #pragma unroll 1
     for (uint32_t round = 0;; ++round) {
       const BwdWork wk = bwd_work(p, round);
@@ -713,8 +735,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
+#if NB_BWD_L2_HINTS
+          tma_reduce_add_3d_hint(&tmap_dq, smem_u32(stage), 0, row, h, keep);
+          tma_reduce_add_3d_hint(&tmap_dq, smem_u32(stage + kTileBytes), 32, row, h, keep);
+#else
           tma_reduce_add_3d(&tmap_dq, smem_u32(stage), 0, row, h);
           tma_reduce_add_3d(&tmap_dq, smem_u32(stage + kTileBytes), 32, row, h);
+#endif
           bulk_commit_group();
         }
         ++s;

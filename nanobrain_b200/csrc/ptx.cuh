@@ -159,6 +159,43 @@ __device__ __forceinline__ void tma_reduce_add_3d(const CUtensorMap* tmap, uint3
       : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_src)
       : "memory");
 }
+// L2 eviction-priority policies. They are hints attached to single accesses (no cache state is
+// configured): the fp32 dQ accumulator is cleared, added into and read back within one backward
+// call and fits the L2, so its lines are marked "evict last" while the call runs and "evict first"
+// on their final read.
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void st_global_v4_hint(void* ptr, float4 v, uint64_t pol) {
+  asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(ptr), "f"(v.x), "f"(v.y),
+               "f"(v.z), "f"(v.w), "l"(pol)
+               : "memory");
+}
+__device__ __forceinline__ float4 ld_global_v4_hint(const void* ptr, uint64_t pol) {
+  float4 v;
+  asm volatile("ld.global.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(ptr), "l"(pol)
+               : "memory");
+  return v;
+}
+// The add-reduction above with an L2 policy.
+__device__ __forceinline__ void tma_reduce_add_3d_hint(const CUtensorMap* tmap, uint32_t smem_src, int c0, int c1,
+                                                       int c2, uint64_t pol) {
+  asm volatile(
+      "cp.reduce.async.bulk.tensor.3d.global.shared::cta.add.tile.bulk_group.L2::cache_hint [%0, {%1, %2, %3}], "
+      "[%4], %5;"
+      :
+      : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(smem_src), "l"(pol)
+      : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until the shared-memory sources of all committed bulk groups have been read.
 __device__ __forceinline__ void bulk_wait_group_read0() {
