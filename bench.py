@@ -41,7 +41,7 @@ NOMINAL_BF16_TFLOPS = 2250.0
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_bwd_kernel launch, from an ncu capture of
 # this workload (only known for that workload; not measured by the run itself).
-NCU_DRAM_BYTES_BWD_MAIN = {"vitb_encoder_varlen": 606.9e6}
+NCU_DRAM_BYTES_BWD_MAIN = {"vitb_encoder_varlen": 600.6e6}
 
 
 def parse_args():
@@ -306,7 +306,7 @@ class Problem:
         return 8 * self.q.numel() * 2 + self.ws_bytes
 
 
-PROBE_EVERY = 4  # every 4th timed step carries the events around the backward main kernel
+PROBE_EVERY = 16
 
 
 def time_problem(prob, steps: int, warmup: int, stream, sync_ranks=None):
