@@ -35,8 +35,9 @@
  *    lengths in cu_seqlens (they size tensor maps and the work list); the kernels verify this on
  *    the device and report NB_ATTN_STATUS_BAD_SEQLENS instead of dropping tiles.
  *  - Varlen scheduling: every call turns cu_seqlens into a work list of (sequence, 128-row tile)
- *    items on the device, most expensive items first and ragged last tiles at the end, and
- *    launches one CTA per item and head; the list lives in the call's workspace.
+ *    items on the device, most expensive items first and ragged last tiles at the end; the forward
+ *    launches one CTA per item and head, the backward one persistent CTA per SM that takes the
+ *    (item, head) pairs in list order. The list lives in the call's workspace.
  *  - Varlen padding: cu_seqlens[batch] may be smaller than total_q / total_k (tokens packed into
  *    a buffer of fixed capacity). The rows past the last sequence belong to no sequence; the
  *    kernels write zeros to them in o, dq, dk and dv (and -inf in lse), so every output row is

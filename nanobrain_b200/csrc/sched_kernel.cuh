@@ -2,8 +2,9 @@
 //
 // In packed (cu_seqlens) mode the attention kernels do not launch a rectangular grid of
 // ceil(max_seqlen / 128) tiles per sequence and let the tiles past a short sequence's end exit;
-// they launch one CTA per entry of a compact list of (sequence, tile) items, built on the device
-// from cu_seqlens by the single-CTA kernel below, with no host synchronisation:
+// they work through a compact list of (sequence, tile) items, built on the device from cu_seqlens by
+// the single-CTA kernel below with no host synchronisation (the forward launches one CTA per entry
+// and head, the backward one persistent CTA per SM that takes the entries in order):
 //
 //   * an item is one 128-row tile on the list's "own" side (query tiles for the forward, key
 //     tiles for the backward); its cost is the number of 128-row steps on the other side;

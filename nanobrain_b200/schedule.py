@@ -1,8 +1,9 @@
 """The varlen tile scheduler's work list, seen from Python.
 
 In packed mode every attention call turns ``cu_seqlens`` into a list of (sequence, 128-row tile)
-items on the device -- most expensive items first, ragged last tiles at the end -- and launches
-one CTA per item and head, so that ragged per-sample visible-token counts (the reference's
+items on the device -- most expensive items first, ragged last tiles at the end -- and works through
+it in that order (the forward with one CTA per item and head, the backward with one persistent CTA
+per SM), so that ragged per-sample visible-token counts (the reference's
 ``src/nanobrain/model.py:186-199`` and its per-image eval loop at ``model.py:254-270``) do not
 leave SMs idle. The calls build the list themselves; the functions here expose the same builder
 for inspection and tests, on the host (no GPU needed) and on the device.
