@@ -103,3 +103,18 @@ def test_skewed_length_mixes_match_the_oracle(lengths):
         err = np.abs(a.detach().float().cpu().numpy() - b)
         assert np.isfinite(err).all(), name
         assert err.max() <= MAX_ABS * max(1.0, np.abs(b).max()) and err.mean() <= MEAN_ABS, (name, err.max(), err.mean())
+
+
+def test_many_short_units_per_persistent_cta_match_the_oracle():
+    # 500 sequences of 1..300 tokens and 3 heads: about 2400 backward work units of one, two or three
+    # steps for the 148 persistent CTAs, so that every CTA runs a dozen units back to back (K buffer
+    # alternation, one-step units, dV / dK leaving while the next unit has started) and the forward
+    # runs several waves of short CTAs.
+    g = torch.Generator().manual_seed(7)
+    lengths = torch.randint(1, 301, (500,), generator=g)
+    got, want = run_varlen(lengths, heads=3, seed=11)
+    for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
+        err = np.abs(a.detach().float().cpu().numpy() - b)
+        assert np.isfinite(err).all(), name
+        assert err.max() <= MAX_ABS * max(1.0, np.abs(b).max()) and err.mean() <= MEAN_ABS, (name, err.max(), err.mean())
+
