@@ -629,9 +629,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
     // the end of the sequence are staged as exact zeros, so adding them is harmless. dV / dK: when
     // the item's last MMA into the accumulator is complete every lane pulls its row into registers
     // as bf16 and the warp stores the rows through a 2 KB scratch area; the issuers start the next
-    // item's first dV / dK MMA as soon as the accumulator has been read. dV is complete half a step before the item's last dQ tile, so it is taken out
-    // before that tile is drained; dK follows the tile. (With both after it, every item's second
-    // step waited ~2900 cycles for the next dV / dK MMA.)
+    // item's first dV / dK MMA as soon as the accumulator has been read. dV is complete half a step
+    // before the item's last dQ tile, so it is taken out before that tile is drained; dK follows the
+    // tile. (With both after it, every item's second step waited ~2900 cycles for the next dV / dK
+    // MMA.)
     setmaxnreg_dec<kBwdDrainRegs>();
     const int quad = warp & 3;
     const uint32_t lane_off = uint32_t(quad * 32) << 16;
